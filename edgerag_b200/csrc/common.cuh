@@ -1,0 +1,120 @@
+// Shared helpers of the sm_100a kernels: element conversion, reductions, error reporting.
+//
+// Every exported function is `extern "C"`, takes raw device pointers and a stream, launches on
+// that stream, allocates nothing, and returns 0 or a negative code whose text `erb_last_error()`
+// gives.  Each source is compiled twice, into one library per element type (float for the 32-bit
+// path, bfloat16 for serving), so a run builds and loads only the type it uses.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+// Each source is compiled once per element type: -DERB_ELEM=0 (float) or 1 (bfloat16).
+#ifndef ERB_ELEM
+#error "compile with -DERB_ELEM=0 (float) or -DERB_ELEM=1 (bfloat16)"
+#endif
+#if ERB_ELEM == 0
+typedef float elem_t;
+#else
+typedef __nv_bfloat16 elem_t;
+#endif
+
+#define ERB_OK 0
+#define ERB_ERR_ARG -1
+#define ERB_ERR_CUDA -2
+#define ERB_ERR_UNSUPPORTED -3
+
+namespace erb {
+
+// One message buffer per library; written by the host wrappers only.
+inline char* error_buffer() {
+  static thread_local char buf[512];
+  return buf;
+}
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return ERB_OK;
+}
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ float round(float v) { return v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+// Loads `N` consecutive elements (N * sizeof(T) must be 16 bytes, pointer 16-byte aligned) as floats.
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* out) {
+  uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load4(const float* p, float* out) {
+  float4 raw = *reinterpret_cast<const float4*>(p);
+  out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block in a fixed order (warp trees, then the first warp over the warp sums);
+// every thread gets the result.  `scratch` holds 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarp) ? scratch[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarp) ? scratch[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+}  // namespace erb
+
+#define ERB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Each library exports its own copy under a library-specific name via this macro.
+#define ERB_DEFINE_LAST_ERROR(name) \
+  ERB_EXPORT const char* name() { return erb::error_buffer(); }

@@ -1,0 +1,286 @@
+"""The Python entry point: a model folder in, generated tokens out.
+
+Assembly follows the reference's ``build_stack`` (bench/serving.py:159-279): configuration and
+weights, one page pool sized from a block count or a memory budget, a scheduler over it, the step
+function under it.  Driving follows the threadless loop of the reference's tests
+(tests/test_executor.py:54-70): ``schedule -> execute -> bookkeeping`` per step, without the worker
+thread and queues of ``InferenceEngine`` (edgerag/serve/engine.py:107-281), which belong to its
+HTTP server.
+
+    engine = Engine.from_pretrained("model_dir", dtype="bfloat16")
+    outputs = engine.generate([[1, 2, 3]], SamplingParams(max_new_tokens=16))
+"""
+
+from __future__ import annotations
+
+import json
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any
+
+import torch
+
+from ..cache.device import DevicePools
+from ..cache.manager import CacheManager, OutOfPagesError
+from ..config.registry import architecture_of, read_model_folder
+from ..models.decoder import DecoderModel
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from ..weights.loader import load_safetensors, random_tensors
+from .request import Request, RequestState
+from .scheduler import Batch, Scheduler, SchedulerConfig
+from .step import ModelRunner, StepEntry
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+GIB = 1024 ** 3
+
+
+def resolve_dtype(dtype: str | torch.dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {dtype} is not bfloat16 or float32")
+        return dtype
+    try:
+        return DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype {dtype!r} is not one of {sorted(DTYPES)}") from None
+
+
+def require_cuda(device: str | torch.device) -> torch.device:
+    """The engine has no CPU path: fail with a clear message instead of falling back."""
+    device = torch.device(device)
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError(f"edgerag_b200 runs on a CUDA device only; asked for {device}, "
+                           f"cuda available: {torch.cuda.is_available()}")
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return device
+
+
+@dataclass
+class EngineOptions:
+    """Engine knobs.  Names follow the reference's CLI and ``SchedulerConfig`` where it has them
+    (scripts/serve_rag.py:104-131, edgerag/sched/scheduler.py:40-49)."""
+
+    dtype: str | torch.dtype = "bfloat16"
+    device: str = "cuda:0"
+    block_size: int = 16                # tokens per cache page
+    num_blocks: int | None = None       # pages in the pool; None: size it from the budget or fraction
+    budget_gib: float | None = None     # total device memory the engine may use (weights included)
+    kv_fraction: float = 0.8            # else: this share of the memory that is free after loading
+    max_batch_size: int = 8
+    chunk_size: int = 512               # prompt tokens per request per step
+    max_prefills_per_step: int = 1
+    max_step_tokens: int | None = None
+    max_model_len: int | None = None
+    reserve_blocks: int = 0
+    eos_token_id: int | None = None
+    overcommit: bool = False
+    seed: int = 0
+    cuda_graphs: bool = True
+    poison_freed_pages: bool = False    # tests: NaN in free pages, so a stale read shows
+
+
+@dataclass
+class TokenEvent:
+    """One generated token (edgerag/serve/engine.py:43-56)."""
+
+    request_id: str
+    token_id: int
+    index: int
+    finished: bool
+    finish_reason: str | None = None
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, config: Any, options: EngineOptions) -> None:
+        self.model = model
+        self.config = config
+        self.options = options
+        self.device = model.device
+        self.dtype = model.dtype
+        layout = model.cache_layout
+        itemsize = 2 if self.dtype == torch.bfloat16 else 4
+        max_len = options.max_model_len or getattr(config, "max_position_embeddings", None) or 8192
+        self.max_model_len = max_len
+        if options.num_blocks is not None:
+            num_pages = options.num_blocks
+        else:
+            free, total = torch.cuda.mem_get_info(self.device)
+            if options.budget_gib:
+                used = total - free
+                room = int(options.budget_gib * GIB) - used
+            else:
+                room = int(free * options.kv_fraction)
+            per_page = max(1, layout.bytes_per_token(itemsize) * options.block_size)
+            num_pages = room // per_page
+            if num_pages < 1:
+                raise RuntimeError(f"no memory left for the cache pool ({room} bytes after the weights)")
+        n_pages = [int(num_pages)] * len(layout.groups)
+        max_step = options.max_step_tokens or (options.chunk_size * options.max_prefills_per_step + options.max_batch_size)
+        self.cache = CacheManager(layout, options.block_size, n_pages, max_requests=options.max_batch_size)
+        self.pools = DevicePools(layout, options.block_size, n_pages, options.max_batch_size, self.dtype,
+                                 self.device, poison=options.poison_freed_pages)
+        self.runner = ModelRunner(model, self.cache, self.pools, max_step_tokens=max_step)
+        self.scheduler = Scheduler(self.cache, SchedulerConfig(
+            max_batch_size=options.max_batch_size, prefill_chunk_size=options.chunk_size,
+            max_prefills_per_step=options.max_prefills_per_step, max_step_tokens=max_step,
+            reserve_pages=options.reserve_blocks, eos_token_id=options.eos_token_id,
+            max_model_len=max_len, overcommit=options.overcommit))
+        self.sampler = Sampler(self.device)
+        self._next_id = 0
+        self._requests: dict[str, Request] = {}
+        self.d2h_bytes_last = 0
+
+    # --- construction -------------------------------------------------------------------------------
+
+    @classmethod
+    def from_pretrained(cls, folder: str | Path, options: EngineOptions | None = None, **overrides) -> "Engine":
+        """Build from a folder with ``config.json`` and ``model.safetensors``."""
+        options = _with(options, overrides)
+        device, dtype = require_cuda(options.device), resolve_dtype(options.dtype)
+        arch, config = read_model_folder(folder)
+        plan = arch.make_plan(config)
+        with torch.cuda.device(device):
+            model = DecoderModel(plan, dtype, device)
+            tensors = load_safetensors(folder, model.weight_specs(), dtype, device,
+                                       plan.name_prefixes, plan.ignored_prefixes)
+            model.load_weights(tensors)
+            del tensors
+            return cls(model, config, options)
+
+    @classmethod
+    def from_config(cls, raw_config: dict | str | Path, weights_seed: int = 0, std: float = 0.02,
+                    options: EngineOptions | None = None, **overrides) -> "Engine":
+        """Build with seeded random weights straight in device memory (no model folder)."""
+        options = _with(options, overrides)
+        device, dtype = require_cuda(options.device), resolve_dtype(options.dtype)
+        if not isinstance(raw_config, dict):
+            raw_config = json.loads(Path(raw_config).read_text())
+        arch = architecture_of(raw_config)
+        config = arch.read_config(raw_config, "config")
+        plan = arch.make_plan(config)
+        with torch.cuda.device(device):
+            model = DecoderModel(plan, dtype, device)
+            model.load_weights(random_tensors(model.weight_specs(), weights_seed, std, compute_dtype=dtype,
+                                              device=device))
+            return cls(model, config, options)
+
+    # --- requests -----------------------------------------------------------------------------------
+
+    def add_request(self, prompt_token_ids: list[int] | None = None, sampling: SamplingParams | None = None,
+                    prompt_embeds: torch.Tensor | None = None, request_id: str | None = None) -> str:
+        """Queue a prompt given as token ids, or as embedding rows ``[prompt_len, hidden]``."""
+        sampling = sampling or SamplingParams()
+        if prompt_embeds is not None:
+            if prompt_embeds.dim() == 3 and prompt_embeds.shape[0] == 1:
+                prompt_embeds = prompt_embeds[0]   # the reference's (1, P, H) layout
+            if prompt_embeds.dim() != 2 or prompt_embeds.shape[1] != self.model.hidden_size:
+                raise ValueError(f"prompt_embeds must be [prompt_len, {self.model.hidden_size}]")
+            if prompt_token_ids is None:
+                prompt_token_ids = [0] * prompt_embeds.shape[0]
+            if len(prompt_token_ids) != prompt_embeds.shape[0]:
+                raise ValueError("prompt_token_ids and prompt_embeds disagree in length")
+            prompt_embeds = prompt_embeds.to(device=self.device, dtype=self.dtype)
+        if prompt_token_ids is None:
+            raise ValueError("a request needs prompt_token_ids or prompt_embeds")
+        ids = [int(t) for t in prompt_token_ids]
+        if prompt_embeds is None and any(not 0 <= t < self.model.vocab_size for t in ids):
+            raise ValueError(f"a prompt token id is outside [0, {self.model.vocab_size})")
+        rid = request_id if request_id is not None else f"req-{self._next_id}"
+        if rid in self._requests and not self._requests[rid].is_finished:
+            raise ValueError(f"request id {rid!r} is in use")
+        seed = sampling.seed if sampling.seed is not None else self.options.seed * 1000003 + self._next_id
+        self._next_id += 1
+        request = Request(rid, ids, sampling, prompt_embeds, seed=seed)
+        self._requests[rid] = request
+        self.scheduler.add_request(request)
+        return rid
+
+    def request(self, request_id: str) -> Request:
+        return self._requests[request_id]
+
+    @property
+    def has_work(self) -> bool:
+        return self.scheduler.has_work
+
+    # --- one iteration ------------------------------------------------------------------------------
+
+    def _entries(self, batch: Batch) -> list[StepEntry]:
+        entries = []
+        for e in batch.entries:
+            r = e.request
+            want = [e.n_tokens - 1] if e.samples else []
+            if e.from_embeds:
+                entries.append(StepEntry(r.request_id, embeds=r.prompt_embeds[e.start: e.start + e.n_tokens], want=want))
+            else:
+                entries.append(StepEntry(r.request_id, tokens=[r.token_at(i) for i in range(e.start, e.start + e.n_tokens)],
+                                         want=want))
+        return entries
+
+    def step(self) -> list[TokenEvent]:
+        """Schedule, run and sample one batch.  Returns the tokens generated in this step."""
+        batch = self.scheduler.schedule()
+        if batch.is_empty:
+            return []
+        try:
+            logits = self.runner.step(self._entries(batch))
+        except Exception as exc:
+            # Every request of the batch fails and frees its pages; the engine stays usable
+            # (edgerag/serve/engine.py:178-189).
+            for e in batch.entries:
+                self.scheduler.abort(e.request, f"error: {type(exc).__name__}")
+            raise
+        sampled = [e for e in batch.entries if e.samples]
+        new_tokens: dict[str, int] = {}
+        if sampled:
+            tokens = self.sampler.sample(
+                logits, [e.request.sampling for e in sampled], [e.request.seed for e in sampled],
+                [e.request.num_generated for e in sampled])
+            new_tokens = {e.request.request_id: t for e, t in zip(sampled, tokens)}
+            self.d2h_bytes_last = 4 * len(tokens)
+        self.scheduler.update(batch, new_tokens)
+        events = []
+        for e in sampled:
+            r = e.request
+            events.append(TokenEvent(r.request_id, new_tokens[r.request_id], r.num_generated - 1,
+                                     r.state == RequestState.FINISHED, r.finish_reason))
+        return events
+
+    def generate(self, prompts: list[list[int]] | None = None, sampling: SamplingParams | list[SamplingParams] | None = None,
+                 prompt_embeds: list[torch.Tensor | None] | None = None) -> list[list[int]]:
+        """Generate for every prompt (token ids, or embeddings where ``prompt_embeds[i]`` is given)
+        and return the new token ids of each, in the order of the prompts."""
+        n = len(prompts) if prompts is not None else len(prompt_embeds or [])
+        params = sampling if isinstance(sampling, list) else [sampling or SamplingParams()] * n
+        ids = []
+        for i in range(n):
+            emb = prompt_embeds[i] if prompt_embeds is not None else None
+            ids.append(self.add_request(prompts[i] if prompts is not None else None, params[i], emb))
+        while self.scheduler.has_work:
+            before = self.scheduler.step_index
+            self.step()
+            if self.scheduler.step_index == before and not self.scheduler.running:
+                break  # nothing could be scheduled: what is left waits for pages that never come
+        out = []
+        for rid in ids:
+            r = self._requests[rid]
+            if r.state == RequestState.REJECTED:
+                raise RuntimeError(f"request {rid} was rejected: {r.finish_reason}")
+            out.append(list(r.generated_token_ids))
+        return out
+
+    def stats(self) -> dict[str, Any]:
+        return {"scheduler": self.scheduler.to_dict(), "cache": self.cache.to_dict(),
+                "pool_bytes": self.pools.nbytes(), "workspace_bytes": self.runner.workspace.nbytes()}
+
+
+def _with(options: EngineOptions | None, overrides: dict) -> EngineOptions:
+    options = options or EngineOptions()
+    if overrides:
+        unknown = set(overrides) - set(options.__dataclass_fields__)
+        if unknown:
+            raise TypeError(f"unknown engine options: {sorted(unknown)}")
+        options = EngineOptions(**{**options.__dict__, **overrides})
+    return options

@@ -1,0 +1,299 @@
+"""The step function: one ragged batch of (request, its next tokens) through the model, from the cache.
+
+The reference's ``ModelExecutor.execute`` (edgerag/serve/executor.py:112-156) runs every request of
+a batch as a forward pass of its own with batch size 1.  Here all entries of a step form **one**
+batch: portions of prompts of any length beside single decoded tokens, flattened to ``T`` tokens
+with, per token, its id (or embedding row), logical position, sequence and cache slot, and per
+sequence a block table.  Only the tokens given are run; everything earlier comes from the cache.
+The result is the float32 logits at the places asked for, in the order of the entries and of
+``want`` inside each entry; sampling sits above (the reference takes the argmax inside the
+executor, edgerag/serve/executor.py:136,154).
+
+Positions are logical and continue from the request's cached length (edgerag/core/model.py:112-120).
+Entries with a single token are placed first inside the batch so that the split-KV decode kernel
+and the row kernel each see a contiguous range; the caller's order is restored in the result.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache.device import DevicePools
+from ..cache.manager import CacheManager, OutOfPagesError
+from ..ops import kernels
+
+
+class StepError(ValueError):
+    """A step was asked for that cannot run (unknown request, bad ids, no room in the batch)."""
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request: ids, or rows of embeddings ``[n, hidden]``; never both."""
+
+    request_id: object
+    tokens: list[int] | None = None
+    embeds: torch.Tensor | None = None
+    want: list[int] = field(default_factory=list)
+
+    @property
+    def n_tokens(self) -> int:
+        return len(self.tokens) if self.embeds is None else int(self.embeds.shape[0])
+
+
+class Workspace:
+    """Named scratch buffers that keep their address from step to step (they only ever grow)."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self._bufs: dict[str, torch.Tensor] = {}
+        self.frozen = False  # set while a CUDA graph that uses the buffers is alive
+
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        need = int(np.prod(shape, dtype=np.int64)) * torch.empty((), dtype=dtype).element_size()
+        buf = self._bufs.get(name)
+        if buf is None or buf.numel() < need:
+            if self.frozen and buf is not None:
+                raise StepError(f"workspace buffer {name} would move while a CUDA graph uses it")
+            buf = torch.empty(max(need, 256), dtype=torch.uint8, device=self.device)
+            self._bufs[name] = buf
+        return buf[:need].view(dtype).view(shape)
+
+    def nbytes(self) -> int:
+        return sum(b.numel() for b in self._bufs.values())
+
+
+class StepContext:
+    """What every part sees of one step.  Device tensors are views of one uploaded int32 buffer."""
+
+    def __init__(self, runner: "ModelRunner") -> None:
+        self._runner = runner
+        self.page_size = runner.cache.page_size
+        self.dtype = runner.dtype
+        self.status = runner.status
+        self.n_tokens = self.n_seqs = self.n_decode = self.n_wanted = 0
+        self.token_ids = self.embed_row = self.positions = self.seq_of_token = None
+        self.token_of_seq = self.want_rows = self.state_slots = self.seq_starts = None
+        self.embeds: torch.Tensor | None = None
+        self.slots: list[torch.Tensor] = []
+        self.block_tables: list[torch.Tensor] = []
+        #: host copies for parts that size launches or loop over sequences
+        self.host_q_len: list[int] = []
+        self.host_positions_last: list[int] = []   # position of each sequence's last token of the step
+        self.host_state_slots: list[int] = []
+
+    def buf(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        return self._runner.workspace.get(name, shape, dtype)
+
+    def pages_of(self, cache_layer: int) -> tuple[torch.Tensor, torch.Tensor]:
+        return self._runner.pools.pages_of(cache_layer)
+
+    def group_of(self, cache_layer: int) -> int:
+        return self._runner.cache.layout.placement[cache_layer][0]
+
+    def state(self, name: str, cache_layer: int) -> torch.Tensor:
+        """The state tensor ``[slots, ...]`` a mixer registered under ``name`` for a cache layer."""
+        return self._runner.pools.states[f"{name}@{cache_layer}"]
+
+    def decode_splits(self, window: int, split_keys: int = kernels.DECODE_SPLIT_KEYS) -> int:
+        """Largest number of key splits any single-token sequence of the batch has."""
+        if self._runner.fixed_decode_splits is not None:
+            return self._runner.fixed_decode_splits
+        most = 1
+        for pos in self.host_positions_last[: self.n_decode]:
+            lo = max(0, pos - window + 1) if window > 0 else 0
+            most = max(most, pos // split_keys - lo // split_keys + 1)
+        return most
+
+
+class ModelRunner:
+    """Owns the model, the cache and the scratch of one device, and runs steps on them."""
+
+    def __init__(self, model, cache: CacheManager, pools: DevicePools, max_step_tokens: int,
+                 check_status: bool = False) -> None:
+        self.model = model
+        self.cache = cache
+        self.pools = pools
+        self.device = pools.device
+        self.dtype = model.dtype
+        self.max_step_tokens = max_step_tokens
+        self.check_status = check_status
+        self.workspace = Workspace(self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.fixed_decode_splits: int | None = None
+        self._meta_dev: torch.Tensor | None = None
+        #: pinned staging buffers, used in turn; each waits for its last upload before it is rewritten
+        self._meta_host: list[torch.Tensor | None] = [None] * 4
+        self._meta_event: list[torch.cuda.Event | None] = [None] * 4
+        self._meta_turn = 0
+        self.steps_run = 0
+        self.h2d_bytes_last = 0
+
+    # --- metadata buffer --------------------------------------------------------------------------
+
+    def _upload(self, flat: np.ndarray) -> torch.Tensor:
+        """Copy the step's int32 metadata to the device through pinned memory (one transfer)."""
+        n = flat.size
+        if self._meta_dev is None or self._meta_dev.numel() < n:
+            if self.workspace.frozen:
+                raise StepError("the metadata buffer would move while a CUDA graph uses it")
+            self._meta_dev = torch.empty(max(4096, 2 * n), dtype=torch.int32, device=self.device)
+        i = self._meta_turn = (self._meta_turn + 1) % len(self._meta_host)
+        if self._meta_event[i] is not None:
+            self._meta_event[i].synchronize()
+        if self._meta_host[i] is None or self._meta_host[i].numel() < n:
+            self._meta_host[i] = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
+        host = self._meta_host[i]
+        host[:n].copy_(torch.from_numpy(flat))
+        self._meta_dev[:n].copy_(host[:n], non_blocking=True)
+        if self._meta_event[i] is None:
+            self._meta_event[i] = torch.cuda.Event()
+        self._meta_event[i].record()
+        self.h2d_bytes_last = 4 * n
+        return self._meta_dev
+
+    # --- the step ---------------------------------------------------------------------------------
+
+    def prepare(self, entries: list[StepEntry]) -> tuple[StepContext, list[StepEntry]]:
+        """Validate, make room in the cache, and upload the batch's metadata.  Nothing is run yet."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        vocab, hidden = self.model.vocab_size, self.model.hidden_size
+        seen = set()
+        for e in entries:
+            if e.request_id not in self.cache.requests:
+                raise StepError(f"request {e.request_id!r} is not admitted")
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if (e.tokens is None) == (e.embeds is None):
+                raise StepError(f"request {e.request_id!r}: pass exactly one of tokens or embeds")
+            n = e.n_tokens
+            if n <= 0:
+                raise StepError(f"request {e.request_id!r}: an entry needs at least one token")
+            if e.embeds is not None and (e.embeds.dim() != 2 or e.embeds.shape[1] != hidden):
+                raise StepError(f"request {e.request_id!r}: embeds must be [n, {hidden}]")
+            if e.tokens is not None and not all(0 <= int(t) < vocab for t in e.tokens):
+                raise StepError(f"request {e.request_id!r}: a token id is outside [0, {vocab})")
+            if any(not 0 <= int(w) < n for w in e.want):
+                raise StepError(f"request {e.request_id!r}: a wanted place is outside its {n} tokens")
+        total = sum(e.n_tokens for e in entries)
+        if total > self.max_step_tokens:
+            raise StepError(f"{total} tokens exceed the step limit of {self.max_step_tokens}")
+
+        # Room in every group for all entries, or nothing changes.
+        n_groups = len(self.cache.layout.groups)
+        need = [0] * n_groups
+        for e in entries:
+            for g, n in enumerate(self.cache.pages_to_grow(e.request_id, e.n_tokens)):
+                need[g] += n
+        free = self.cache.free_pages()
+        if any(n > f for n, f in zip(need, free)):
+            raise OutOfPagesError(f"step needs {need} more pages per group, {free} free")
+        for e in entries:
+            self.cache.grow(e.request_id, e.n_tokens)
+
+        # Single-token entries first; a stable order otherwise.
+        order = sorted(range(len(entries)), key=lambda i: (entries[i].n_tokens != 1, i))
+        ordered = [entries[i] for i in order]
+        n_seqs = len(ordered)
+        n_decode = sum(1 for e in ordered if e.n_tokens == 1)
+        ps = self.cache.page_size
+
+        token_ids = np.zeros(total, np.int32)
+        embed_row = np.full(total, -1, np.int32)
+        positions = np.zeros(total, np.int32)
+        seq_of_token = np.zeros(total, np.int32)
+        slots = np.full((n_groups, total), -1, np.int32)
+        token_of_seq = np.zeros(n_seqs, np.int32)
+        seq_starts = np.zeros(n_seqs + 1, np.int32)
+        state_slots = np.zeros(n_seqs, np.int32)
+        max_pages = 1
+        for e in ordered:
+            rc = self.cache.requests[e.request_id]
+            max_pages = max(max_pages, max((len(t.pages) for t in rc.tables), default=1))
+        tables = np.zeros((n_groups, n_seqs, max_pages), np.int32)
+        want_of_entry: dict[int, list[int]] = {}
+        embed_chunks: list[torch.Tensor] = []
+        n_embed_rows = 0
+        ctx = StepContext(self)
+        t0 = 0
+        for s, (orig, e) in enumerate(zip(order, ordered)):
+            rc = self.cache.requests[e.request_id]
+            n = e.n_tokens
+            past = rc.num_tokens
+            sl = slice(t0, t0 + n)
+            positions[sl] = np.arange(past, past + n, dtype=np.int32)
+            seq_of_token[sl] = s
+            if e.embeds is None:
+                token_ids[sl] = np.asarray(e.tokens, dtype=np.int32)
+            else:
+                embed_row[sl] = np.arange(n_embed_rows, n_embed_rows + n, dtype=np.int32)
+                embed_chunks.append(e.embeds)
+                n_embed_rows += n
+            for g, row in enumerate(self.cache.slots_for(e.request_id, n)):
+                slots[g, sl] = row
+                pages = rc.tables[g].pages
+                tables[g, s, : len(pages)] = [p if p >= 0 else 0 for p in pages]
+            token_of_seq[s] = t0
+            seq_starts[s + 1] = t0 + n
+            state_slots[s] = rc.slot
+            want_of_entry[orig] = [t0 + int(w) for w in e.want]
+            ctx.host_q_len.append(n)
+            ctx.host_positions_last.append(past + n - 1)
+            ctx.host_state_slots.append(rc.slot)
+            t0 += n
+        want_rows = np.asarray([r for i in range(len(entries)) for r in want_of_entry[i]], dtype=np.int32)
+
+        pieces = [token_ids, embed_row, positions, seq_of_token, slots.reshape(-1), token_of_seq, seq_starts,
+                  state_slots, want_rows, tables.reshape(-1)]
+        flat = np.concatenate(pieces)
+        dev = self._upload(flat)
+        views, off = [], 0
+        for p in pieces:
+            views.append(dev[off: off + p.size])
+            off += p.size
+        (ctx.token_ids, ctx.embed_row, ctx.positions, ctx.seq_of_token, slots_d, ctx.token_of_seq, ctx.seq_starts,
+         ctx.state_slots, ctx.want_rows, tables_d) = views
+        ctx.slots = [slots_d[g * total: (g + 1) * total] for g in range(n_groups)]
+        per = n_seqs * max_pages
+        ctx.block_tables = [tables_d[g * per: (g + 1) * per].view(n_seqs, max_pages) for g in range(n_groups)]
+        ctx.n_tokens, ctx.n_seqs, ctx.n_decode, ctx.n_wanted = total, n_seqs, n_decode, int(want_rows.size)
+        if embed_chunks:
+            ctx.embeds = torch.cat([c.to(device=self.device, dtype=self.dtype, non_blocking=True)
+                                    for c in embed_chunks], dim=0).contiguous()
+        return ctx, ordered
+
+    def finish(self, ordered: list[StepEntry]) -> None:
+        """Count the step's tokens as written and hand back what windows have passed."""
+        for e in ordered:
+            self.cache.advance(e.request_id, e.n_tokens)
+        self.pools.poison_pages(self.cache.drain_freed())
+
+    @torch.inference_mode()
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Run one batch.  Returns float32 logits ``[wanted, vocab]`` (a view of a buffer that the
+        next step overwrites), or ``None`` when nothing was wanted."""
+        self.pools.zero_slots(self.cache.drain_new_slots())
+        ctx, ordered = self.prepare(entries)
+        logits = self.model.forward(ctx)
+        self.finish(ordered)
+        self.steps_run += 1
+        if self.check_status:
+            code = int(self.status.item())
+            if code:
+                self.status.zero_()
+                raise StepError(f"a kernel flagged token {code - 1} of the batch (id or row out of range)")
+        return logits
+
+    # --- requests ---------------------------------------------------------------------------------
+
+    def admit(self, request_id: object) -> None:
+        self.cache.admit(request_id)
+
+    def release(self, request_id: object) -> None:
+        self.cache.release(request_id)
+        self.pools.poison_pages(self.cache.drain_freed())

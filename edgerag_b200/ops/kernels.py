@@ -1,0 +1,292 @@
+"""Python entry points of the CUDA kernels: tensors in, one launch on the current stream each.
+
+Every function checks what a wrong call would turn into a wrong result (device, dtype, layout,
+sizes), then calls the ``extern "C"`` function of the library built for the tensors' element type.
+Nothing here falls back to PyTorch arithmetic: a missing library or a refused shape raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import native
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or its launch failed."""
+
+
+_ELEM = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
+
+_SIGNATURES = {
+    "erb_embed_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                       c_void_p, c_void_p],
+    "erb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+                        c_void_p],
+    "erb_residual_add": [c_void_p, c_void_p, c_longlong, c_void_p],
+    "erb_rope_cache_write": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_swiglu": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "erb_gather_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "erb_linear": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                   c_void_p, c_longlong, c_void_p],
+    "erb_attention_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "erb_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                             c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_float, c_void_p],
+    "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+}
+
+_functions: dict[tuple[str, str | None, str], object] = {}
+
+
+def _fn(library: str, elem: str | None, name: str):
+    key = (library, elem, name)
+    fn = _functions.get(key)
+    if fn is None:
+        lib = native.load(library, elem)
+        fn = getattr(lib, name)
+        fn.argtypes = _SIGNATURES[name]
+        fn.restype = c_int
+        fn._erb_lib = lib
+        _functions[key] = fn
+    return fn
+
+
+def _call(fn, *args) -> None:
+    rc = fn(*args)
+    if rc != 0:
+        raise KernelError(fn._erb_lib.erb_last_error().decode())
+
+
+def _elem(t: torch.Tensor) -> str:
+    try:
+        return _ELEM[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not float32 or bfloat16") from None
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor | None, name: str, dtype=None, contiguous: bool = True) -> None:
+    if t is None:
+        return
+    if not t.is_cuda:
+        raise KernelError(f"{name} is not on a CUDA device")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+
+
+# --- rows ------------------------------------------------------------------------------------
+
+def embed_rows(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
+               embeds: torch.Tensor | None = None, embed_row: torch.Tensor | None = None) -> None:
+    """hidden[t] = table[ids[t]], or embeds[embed_row[t]] where embed_row[t] >= 0 (float output)."""
+    n, h = hidden.shape
+    _need(hidden, "hidden", torch.float32); _need(table, "table"); _need(ids, "ids", torch.int32)
+    _need(status, "status", torch.int32); _need(embed_row, "embed_row", torch.int32)
+    if table.shape[1] != h or ids.numel() < n:
+        raise KernelError("embed_rows: shapes disagree")
+    if embeds is not None:
+        _need(embeds, "embeds", table.dtype)
+        if embeds.shape[1] != h or embed_row is None:
+            raise KernelError("embed_rows: embeds need embed_row and the hidden width")
+    _call(_fn("elementwise", _elem(table), "erb_embed_rows"), hidden.data_ptr(), table.data_ptr(),
+          _ptr(embeds), ids.data_ptr(), _ptr(embed_row), n, h, table.shape[0],
+          0 if embeds is None else embeds.shape[0], status.data_ptr(), _stream())
+
+
+def add_rmsnorm(hidden: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+                delta: torch.Tensor | None = None, rows: torch.Tensor | None = None,
+                write_back: bool = True) -> None:
+    """out = weight * round(rmsnorm(hidden (+ delta))); hidden += delta in place when write_back."""
+    _need(hidden, "hidden", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    _need(delta, "delta", out.dtype); _need(rows, "rows", torch.int32)
+    h = hidden.shape[1]
+    n = out.shape[0]
+    if out.shape[1] != h or weight.numel() != h or (delta is not None and delta.shape != hidden.shape):
+        raise KernelError("add_rmsnorm: shapes disagree")
+    if rows is None and n != hidden.shape[0]:
+        raise KernelError("add_rmsnorm: out rows differ from hidden rows")
+    if rows is not None and rows.numel() < n:
+        raise KernelError("add_rmsnorm: fewer row indices than output rows")
+    _call(_fn("elementwise", _elem(out), "erb_add_rmsnorm"), hidden.data_ptr(), _ptr(delta), weight.data_ptr(),
+          out.data_ptr(), _ptr(rows), n, h, float(eps), int(write_back and rows is None), _stream())
+
+
+def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(hidden, "hidden", torch.float32); _need(delta, "delta")
+    if hidden.shape != delta.shape:
+        raise KernelError("residual_add: shapes disagree")
+    _call(_fn("elementwise", _elem(delta), "erb_residual_add"), hidden.data_ptr(), delta.data_ptr(),
+          hidden.numel(), _stream())
+
+
+def gather_cast(src: torch.Tensor, dst: torch.Tensor, rows: torch.Tensor | None) -> None:
+    _need(src, "src", torch.float32); _need(dst, "dst"); _need(rows, "rows", torch.int32)
+    _call(_fn("elementwise", _elem(dst), "erb_gather_cast"), src.data_ptr(), dst.data_ptr(), _ptr(rows),
+          dst.shape[0], dst.shape[1], _stream())
+
+
+def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor | None,
+                     n_q_heads: int, n_kv_heads: int, head_dim: int, rot_dim: int,
+                     slots: torch.Tensor | None = None, k_pages: torch.Tensor | None = None,
+                     v_pages: torch.Tensor | None = None, page_size: int = 0) -> None:
+    """Rotate q (in place) and k by the halves convention; write rotated k and v to cache slots.
+
+    ``k_pages``/``v_pages``: one layer's pages ``[n_pages, n_kv_heads, page_size, head_dim]``.
+    ``slots``: int32 per token, ``page * page_size + offset`` or negative to write nothing.
+    """
+    _need(qkv, "qkv"); _need(positions, "positions", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    _need(slots, "slots", torch.int32); _need(k_pages, "k_pages", qkv.dtype); _need(v_pages, "v_pages", qkv.dtype)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_q_heads + 2 * n_kv_heads) * head_dim or positions.numel() < n:
+        raise KernelError("rope_cache_write: qkv width or positions disagree with the head counts")
+    write = k_pages is not None
+    if write:
+        if v_pages is None or slots is None or slots.numel() < n:
+            raise KernelError("rope_cache_write: cache write needs k_pages, v_pages and slots")
+        if tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim) or k_pages.shape != v_pages.shape:
+            raise KernelError("rope_cache_write: page layout is not [pages, kv heads, page_size, head_dim]")
+    if rot_dim and (inv_freq is None or inv_freq.numel() != rot_dim // 2):
+        raise KernelError("rope_cache_write: inv_freq must hold rot_dim / 2 values")
+    _call(_fn("elementwise", _elem(qkv), "erb_rope_cache_write"), qkv.data_ptr(), positions.data_ptr(),
+          _ptr(inv_freq), _ptr(slots), _ptr(k_pages), _ptr(v_pages), n, n_q_heads, n_kv_heads, head_dim,
+          rot_dim, page_size, int(write), _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    n, inter = out.shape
+    if gate_up.shape != (n, 2 * inter):
+        raise KernelError("swiglu: gate_up must be [tokens, 2 * intermediate]")
+    _call(_fn("elementwise", _elem(out), "erb_swiglu"), gate_up.data_ptr(), out.data_ptr(), n, inter, _stream())
+
+
+# --- matrix products -------------------------------------------------------------------------
+
+_workspaces: dict[int, torch.Tensor] = {}
+WORKSPACE_BYTES = 64 << 20
+
+
+def _workspace(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None:
+        ws = torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _workspaces[idx] = ws
+    return ws
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out[M, N] (+)= a[M, K] @ weight[N, K]^T (library product, float accumulation, no TF32).
+
+    ``a`` and ``out`` may be row-strided views (last dimension contiguous); ``out`` is float or the
+    element type of ``a``.
+    """
+    _need(a, "a", contiguous=False); _need(weight, "weight", a.dtype); _need(out, "out", contiguous=False)
+    m, k = a.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or out.shape != (m, n) or a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("linear: shapes or strides disagree")
+    if out.dtype not in (a.dtype, torch.float32):
+        raise KernelError("linear: out must be float32 or the input type")
+    if m == 0:
+        return
+    ws = _workspace(a.device)
+    _call(_fn("gemm", _elem(a), "erb_linear"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+          a.stride(0) if m > 1 else max(k, a.stride(0)), k, out.stride(0) if m > 1 else max(n, out.stride(0)),
+          int(out.dtype == torch.float32), int(accumulate), ws.data_ptr(), ws.numel(), _stream())
+
+
+# --- attention -------------------------------------------------------------------------------
+
+def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                   seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
+                   scale: float, window: int = 0) -> None:
+    """Causal attention of every token over its sequence's pages (general kernel, any portion sizes).
+
+    ``q``: ``[tokens, >= n_q_heads * D]`` view with unit inner stride (the q part of a qkv buffer);
+    ``out``: ``[tokens, n_q_heads * D]``; pages ``[n_pages, n_kv_heads, page_size, D]``;
+    ``block_tables`` int32 ``[sequences, max_pages]``.
+    """
+    _need(q, "q", contiguous=False); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
+    _need(block_tables, "block_tables", torch.int32); _need(seq_of_token, "seq_of_token", torch.int32)
+    _need(positions, "positions", torch.int32); _need(out, "out", q.dtype, contiguous=False)
+    n = q.shape[0]
+    _, nkv, page_size, d = k_pages.shape
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] < n_q_heads * d or out.shape[1] < n_q_heads * d:
+        raise KernelError("attention_rows: q/out layout disagrees with the head counts")
+    _call(_fn("attention", _elem(q), "erb_attention_rows"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
+          v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_of_token.data_ptr(),
+          positions.data_ptr(), out.data_ptr(), out.stride(0), n, n_q_heads, nkv, d, page_size, int(window),
+          float(scale), _stream())
+
+
+DECODE_SPLIT_KEYS = 512
+
+
+def decode_scratch_floats(n_seqs: int, n_q_heads: int, head_dim: int, max_splits: int) -> tuple[int, int]:
+    return n_seqs * n_q_heads * max_splits * head_dim, n_seqs * n_q_heads * max_splits * 2
+
+
+def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                     token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
+                     scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
+                     window: int = 0, split_keys: int = DECODE_SPLIT_KEYS) -> None:
+    """Attention of one new token per sequence, keys cut into splits of ``split_keys`` (split-KV).
+
+    ``token_of_seq`` int32 ``[sequences]`` gives each sequence's row in q/out/positions.  Scratch:
+    ``part_acc`` float ``[sequences * heads * max_splits * D]``, ``part_ml`` twice
+    ``sequences * heads * max_splits``.
+    """
+    _need(q, "q", contiguous=False); _need(k_pages, "k_pages", q.dtype); _need(v_pages, "v_pages", q.dtype)
+    _need(block_tables, "block_tables", torch.int32); _need(token_of_seq, "token_of_seq", torch.int32)
+    _need(positions, "positions", torch.int32); _need(out, "out", q.dtype, contiguous=False)
+    _need(part_acc, "part_acc", torch.float32); _need(part_ml, "part_ml", torch.float32)
+    n_seqs = token_of_seq.numel()
+    _, nkv, page_size, d = k_pages.shape
+    need_acc, need_ml = decode_scratch_floats(n_seqs, n_q_heads, d, max_splits)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
+        raise KernelError("attention_decode: scratch too small")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention_decode: q/out inner stride must be 1")
+    _call(_fn("attention", _elem(q), "erb_attention_decode"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
+          v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
+          positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(),
+          max_splits, n_seqs, n_q_heads, nkv, d, page_size, int(window), int(split_keys), float(scale), _stream())
+
+
+# --- sampling --------------------------------------------------------------------------------
+
+def sample_rows(logits: torch.Tensor, tokens: torch.Tensor, temperature: torch.Tensor | None = None,
+                rng_state: torch.Tensor | None = None) -> None:
+    """tokens[r] = argmax(logits[r]) where temperature[r] <= 0, else an inverse-CDF draw."""
+    _need(logits, "logits", torch.float32, contiguous=False); _need(tokens, "tokens", torch.int32)
+    _need(temperature, "temperature", torch.float32); _need(rng_state, "rng_state", torch.int64)
+    if logits.stride(1) != 1 or tokens.numel() < logits.shape[0]:
+        raise KernelError("sample_rows: layout disagrees")
+    _call(_fn("sampling", None, "erb_sample_rows"), logits.data_ptr(), logits.stride(0) if logits.shape[0] > 1 else max(logits.stride(0), logits.shape[1]),
+          logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(rng_state), tokens.data_ptr(), _stream())
+
+
+def uniform_from_state(state: int) -> float:
+    """The uniform in [0, 1) that the sampling kernel derives from a 64-bit state (host copy)."""
+    z = (state + 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+    z ^= z >> 31
+    return (z >> 40) / 16777216.0

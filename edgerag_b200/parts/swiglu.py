@@ -1,0 +1,40 @@
+"""The gated feed-forward of the Llama decoder: ``down(silu(gate(x)) * up(x))``, no biases
+(edgerag/core/layers.py:332-341).  ``gate`` and ``up`` are stored as one matrix ``[Wg; Wu]`` so a
+single product feeds the gate kernel, which computes ``silu(g) * u`` in float32 and rounds once.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from .base import FeedForward, WeightSpec, register_part
+
+
+@register_part("ffn", "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, hidden: int, intermediate: int, dtype: torch.dtype, device: torch.device) -> None:
+        self.hidden, self.intermediate = hidden, intermediate
+        self.dtype, self.device = dtype, device
+        self.w_gate_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return [WeightSpec("gate_proj.weight", (self.intermediate, self.hidden)),
+                WeightSpec("up_proj.weight", (self.intermediate, self.hidden)),
+                WeightSpec("down_proj.weight", (self.hidden, self.intermediate))]
+
+    def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
+        cast = lambda t: t.to(device=self.device, dtype=self.dtype)  # noqa: E731
+        self.w_gate_up = torch.cat([cast(tensors["gate_proj.weight"]), cast(tensors["up_proj.weight"])], 0).contiguous()
+        self.w_down = cast(tensors["down_proj.weight"]).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        n = x.shape[0]
+        gate_up = ctx.buf("ffn.gate_up", (n, 2 * self.intermediate), self.dtype)
+        kernels.linear(x, self.w_gate_up, gate_up)
+        act = ctx.buf("ffn.act", (n, self.intermediate), self.dtype)
+        kernels.swiglu(gate_up, act)
+        y = ctx.buf("ffn.out", (n, self.hidden), self.dtype)
+        kernels.linear(act, self.w_down, y)
+        return y
