@@ -10,6 +10,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from pathlib import Path
 
 import numpy as np
@@ -74,7 +75,9 @@ class SafetensorsFile:
         dtype, _ = _DTYPES[info["dtype"]]
         begin, end = info["data_offsets"]
         raw = np.frombuffer(self._mmap, dtype=np.uint8, count=end - begin, offset=self._data_start + begin)
-        flat = torch.from_numpy(raw)  # read-only memory; every use below copies
+        with warnings.catch_warnings():
+            warnings.filterwarnings("ignore", message=".*not writable.*")
+            flat = torch.from_numpy(raw)  # read-only memory: callers copy or cast, never write
         return flat.view(dtype).reshape(info["shape"])
 
     def close(self) -> None:

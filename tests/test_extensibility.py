@@ -1,0 +1,149 @@
+"""Parts and architectures are added from outside: a toy mixer with state of its own, defined
+here, is registered, built into a model by a plan, loaded from a folder and stepped, portion by
+portion and beside other requests, without a change to the framework's files."""
+
+from __future__ import annotations
+
+import json
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HIDDEN, VOCAB, LAYERS = 48, 97, 3
+DECAY = 0.9
+
+
+def register_toy():
+    from edgerag_b200.cache.manager import StateSpec
+    from edgerag_b200.config import register_architecture
+    from edgerag_b200.parts.base import (LayerCall, LayerSpec, Mixer, ModelPlan, PartSpec, WeightSpec,
+                                         register_part)
+
+    @register_part("mixer", "toy_decay")
+    class ToyDecayMixer(Mixer):
+        """y_t = W (s_t),  s_t = decay * s_{t-1} + x_t: a running state of fixed size per request."""
+
+        def __init__(self, hidden, decay, dtype, device):
+            self.hidden, self.decay, self.dtype, self.device = hidden, decay, dtype, device
+            self.w = None
+
+        def cache_spec(self):
+            return [StateSpec("toy_state", (self.hidden,), "float32")]
+
+        def weight_specs(self):
+            return [WeightSpec("mix.weight", (self.hidden, self.hidden))]
+
+        def load_weights(self, tensors):
+            self.w = tensors["mix.weight"].to(device=self.device, dtype=self.dtype)
+
+        def forward(self, x, ctx, call):
+            from edgerag_b200.ops import kernels
+
+            state = ctx.state("toy_state", call.cache_layer)         # [slots, hidden]
+            out = ctx.buf("toy.s", (x.shape[0], self.hidden), self.dtype)
+            t0 = 0
+            for s, n in enumerate(ctx.host_q_len):                    # each request's slot is updated once per step
+                slot = ctx.host_state_slots[s]
+                cur = state[slot]
+                for t in range(t0, t0 + n):
+                    cur = self.decay * cur + x[t].float()
+                    out[t] = cur.to(self.dtype)
+                state[slot] = cur
+                t0 += n
+            y = ctx.buf("toy.y", (x.shape[0], self.hidden), self.dtype)
+            kernels.linear(out, self.w, y)
+            return y
+
+    def read_config(raw, where):
+        return raw
+
+    def make_plan(raw):
+        h = raw["hidden_size"]
+        norm = lambda p: PartSpec("rmsnorm", {"size": h, "eps": raw["eps"]}, p)   # noqa: E731
+        layers = []
+        for i in range(raw["num_hidden_layers"]):
+            if i % 2 == 0:
+                mixer = PartSpec("toy_decay", {"hidden": h, "decay": raw["decay"]}, "toy.")
+            else:   # a different mixer in a different layer of the same model
+                mixer = PartSpec("attention", {"hidden": h, "n_q_heads": 2, "n_kv_heads": 1, "head_dim": 16,
+                                               "position": PartSpec("rope_halves", {"head_dim": 16, "theta": 1000.0})}, "self_attn.")
+            layers.append(LayerSpec(f"layers.{i}.", PartSpec("prenorm"), norm("ln1."), mixer, norm("ln2."),
+                                    PartSpec("swiglu", {"hidden": h, "intermediate": 2 * h}, "mlp.")))
+        return ModelPlan(h, raw["vocab_size"], PartSpec("table", {"vocab": raw["vocab_size"], "hidden": h}, "embed_tokens."),
+                         layers, [LayerCall(i, i) for i in range(len(layers))], norm("norm."),
+                         PartSpec("linear", {"vocab": raw["vocab_size"], "hidden": h, "tied": True}, "lm_head."))
+
+    register_architecture("ToyDecayForCausalLM", read_config, make_plan)
+
+
+def plain_toy(weights, raw, ids):
+    """Whole-sequence float32 computation of the toy model, written out with no engine code."""
+    import plain_llama as plain
+
+    h = weights["model.embed_tokens.weight"][torch.tensor(ids)]
+    n = h.shape[0]
+    for i in range(raw["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        x = plain.rms_norm(h, weights[p + "ln1.weight"], raw["eps"])
+        if i % 2 == 0:
+            s, rows = torch.zeros(raw["hidden_size"]), []
+            for t in range(n):
+                s = raw["decay"] * s + x[t]
+                rows.append(s)
+            h = h + torch.stack(rows) @ weights[p + "toy.mix.weight"].T
+        else:
+            cfg = {"head_dim": 16, "n_q": 2, "n_kv": 1, "theta": 1000.0}
+            a = p + "self_attn."
+            h = h + plain.attention(x, torch.arange(n), weights[a + "q_proj.weight"], weights[a + "k_proj.weight"],
+                                    weights[a + "v_proj.weight"], weights[a + "o_proj.weight"], cfg)
+        y = plain.rms_norm(h, weights[p + "ln2.weight"], raw["eps"])
+        m = p + "mlp."
+        h = h + plain.swiglu(y, weights[m + "gate_proj.weight"], weights[m + "up_proj.weight"], weights[m + "down_proj.weight"])
+    return plain.rms_norm(h, weights["model.norm.weight"], raw["eps"]) @ weights["model.embed_tokens.weight"].T
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    register_toy()
+    from edgerag_b200 import Engine
+    from edgerag_b200.config.registry import architecture_of
+    from edgerag_b200.engine.step import StepEntry
+    from edgerag_b200.models.decoder import DecoderModel
+    from edgerag_b200.weights.loader import write_model_folder
+    import plain_llama as plain
+
+    raw = {"architectures": ["ToyDecayForCausalLM"], "hidden_size": HIDDEN, "vocab_size": VOCAB,
+           "num_hidden_layers": LAYERS, "eps": 1e-5, "decay": DECAY}
+    arch = architecture_of(raw)
+    specs = DecoderModel(arch.make_plan(raw), torch.float32, torch.device("cpu")).weight_specs()
+    folder = write_model_folder(tmp_path / "toy", raw, specs, seed=11, std=0.15, norm_jitter=0.1, dtype=torch.float32)
+    engine = Engine.from_pretrained(folder, dtype="float32", block_size=4, num_blocks=40, max_batch_size=3)
+    layout = engine.model.cache_layout
+    assert [s.name for s in layout.states] == ["toy_state@0", "toy_state@2"] and len(layout.groups) == 1
+    assert layout.placement == [None, (0, 0), None]
+
+    weights = plain.read_weights(folder)
+    seqs = {"x": torch.randint(0, VOCAB, (23,), generator=torch.Generator().manual_seed(1)).tolist(),
+            "y": torch.randint(0, VOCAB, (11,), generator=torch.Generator().manual_seed(2)).tolist()}
+    want = {k: plain_toy(weights, raw, v) for k, v in seqs.items()}
+    runner = engine.runner
+    runner.admit("x"), runner.admit("y")
+    got = {"x": [], "y": []}
+    fed = {"x": 0, "y": 0}
+    plan = [{"x": 5}, {"x": 2, "y": 4}, {"x": 1, "y": 1}, {"y": 6}, {"x": 15}]
+    for step in plan:
+        entries = [StepEntry(k, tokens=seqs[k][fed[k]: fed[k] + n], want=list(range(n))) for k, n in step.items()]
+        logits = runner.step(entries).cpu()
+        row = 0
+        for k, n in step.items():
+            got[k].append(logits[row: row + n])
+            row += n
+            fed[k] += n
+    for k in seqs:
+        torch.testing.assert_close(torch.cat(got[k]), want[k], atol=2e-4, rtol=2e-4)
+    # a released slot starts from zero for the next request
+    runner.release("x")
+    runner.admit("z")
+    again = runner.step([StepEntry("z", tokens=seqs["x"], want=[22])]).cpu()
+    torch.testing.assert_close(again[0], want["x"][22], atol=2e-4, rtol=2e-4)

@@ -1,0 +1,128 @@
+"""Generation through the Python entry point and the command line, against the plain implementation."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def margins_ok(weights, cfg, prompt, tokens, min_margin):
+    """Positions whose top-2 margin in the plain logits exceeds ``min_margin`` must agree
+    (the reference's rule for 16-bit runs, tests/test_equivalence.py:260-324)."""
+    seq = list(prompt)
+    for t in tokens:
+        logits = plain.forward(weights, cfg, seq)[-1]
+        top = torch.topk(logits, 2).values
+        if float(top[0] - top[1]) > min_margin:
+            assert t == int(logits.argmax()), (len(seq) - len(prompt), t, int(logits.argmax()))
+            seq.append(t)
+        else:
+            return   # a near-tie: the two runs may part ways from here on
+    return
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_greedy_generation_matches_plain(which, dtype, model_folders):
+    from edgerag_b200 import Engine, SamplingParams
+
+    folder = model_folders(which, dtype, std=0.2)     # larger weights: decisive logits
+    cfg, weights = plain.read_config(folder), plain.read_weights(folder)
+    prompts = [helpers.random_sequence(cfg["vocab"], n, 40 + n) for n in ((7, 33) if which == "a" else (5, 40, 77))]
+    engine = Engine.from_pretrained(folder, dtype=dtype, block_size=16 if which == "a" else 8, num_blocks=64,
+                                    chunk_size=16, max_batch_size=3, poison_freed_pages=True)
+    outs = engine.generate(prompts, SamplingParams(max_new_tokens=16))
+    assert engine.cache.free_pages() == [64] and not engine.has_work
+    for prompt, out in zip(prompts, outs):
+        assert len(out) == 16
+        if dtype == "float32":
+            assert out == plain.greedy_generate(weights, cfg, prompt, 16)
+        else:
+            margins_ok(weights, cfg, prompt, out, min_margin=0.05 * float(plain.forward(weights, cfg, prompt)[-1].abs().max()))
+    # chunk size and batch composition do not change the tokens (tests/test_executor.py:120-191)
+    engine2 = Engine.from_pretrained(folder, dtype=dtype, block_size=4, num_blocks=200, chunk_size=5, max_batch_size=1)
+    if dtype == "float32":
+        assert engine2.generate(prompts, SamplingParams(max_new_tokens=16)) == outs
+
+
+def test_prompt_embeds_temperature_and_eos(model_folders):
+    from edgerag_b200 import Engine, SamplingParams
+    from edgerag_b200.ops.kernels import uniform_from_state
+    from edgerag_b200.sampling.params import rng_state
+
+    folder = model_folders("b", "float32", std=0.2)
+    cfg, weights = plain.read_config(folder), plain.read_weights(folder)
+    engine = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=64, chunk_size=16, max_batch_size=4)
+    prompt = helpers.random_sequence(cfg["vocab"], 20, 9)
+    rows = plain.embed(weights, torch.tensor(prompt))
+    by_ids, by_rows = engine.generate([prompt, None], SamplingParams(max_new_tokens=8), prompt_embeds=[None, rows])
+    assert by_ids == by_rows == plain.greedy_generate(weights, cfg, prompt, 8)
+    # N(0, 1) rows that are no token's embedding, with temperature 0.7 and a seed: every draw is where the
+    # plain distribution and the request's own uniform put it, whatever else runs beside it
+    emb = torch.randn((20, cfg["hidden"]), generator=torch.Generator().manual_seed(1))
+    params = SamplingParams(temperature=0.7, seed=1, max_new_tokens=6)
+    alone = engine.generate(None, params, prompt_embeds=[emb])[0]
+    mixed = engine.generate([prompt, None, prompt[:5]], [SamplingParams(max_new_tokens=9), params, SamplingParams(max_new_tokens=3)],
+                            prompt_embeds=[None, emb, None])
+    assert mixed[1] == alone and mixed[0][:8] == by_ids
+    h = emb
+    for i, token in enumerate(alone):
+        logits = plain.forward(weights, cfg, embeds=h)[-1]
+        cdf = torch.cumsum(plain.temperature_probs(logits, 0.7), 0)
+        u = uniform_from_state(rng_state(1, i))
+        lo = float(cdf[token - 1]) if token else 0.0
+        assert lo - 1e-4 <= u < float(cdf[token]) + 1e-4
+        h = torch.cat([h, plain.embed(weights, torch.tensor([token]))])
+    # an end-of-sequence id stops a request early and frees its pages
+    first = by_ids[2]
+    stopper = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=64, eos_token_id=first)
+    out = stopper.generate([prompt], SamplingParams(max_new_tokens=8))[0]
+    assert out == by_ids[:3] and stopper.request("req-0").finish_reason == "stop"
+    assert stopper.cache.free_pages() == [64]
+
+
+def test_preemption_recomputes_to_the_same_tokens(model_folders):
+    """With admission by current size and a pool too small for both requests, the newer one is
+    evicted, recomputed later, and still produces the tokens it produces alone."""
+    from edgerag_b200 import Engine, SamplingParams
+
+    folder = model_folders("a", "float32", std=0.2)
+    cfg = plain.read_config(folder)
+    prompts = [helpers.random_sequence(cfg["vocab"], 30, 1), helpers.random_sequence(cfg["vocab"], 30, 2)]
+    roomy = Engine.from_pretrained(folder, dtype="float32", block_size=16, num_blocks=32)
+    want = roomy.generate(prompts, SamplingParams(max_new_tokens=40))
+    tight = Engine.from_pretrained(folder, dtype="float32", block_size=16, num_blocks=7, overcommit=True,
+                                   max_prefills_per_step=2, poison_freed_pages=True)
+    got = tight.generate(prompts, SamplingParams(max_new_tokens=40))
+    assert tight.scheduler.stats.preempted >= 1 and got == want
+    assert tight.cache.free_pages() == [7]
+
+
+def test_command_line(model_folders, tmp_path):
+    folder = model_folders("a", "float32", std=0.2)
+    cfg, weights = plain.read_config(folder), plain.read_weights(folder)
+    prompt = helpers.random_sequence(cfg["vocab"], 12, 3)
+    cmd = [sys.executable, "-m", "edgerag_b200", "--model", str(folder), "--dtype", "fp32", "--num-blocks", "32",
+           "--chunk-size", "8", "--max-new-tokens", "6", "--prompt-ids", ",".join(map(str, prompt)), "--json"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=str(helpers.ROOT))
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    out = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert out["outputs"][0]["token_ids"] == plain.greedy_generate(weights, cfg, prompt, 6)
+    # random-weights mode: writes a folder and generates from it
+    conf = tmp_path / "config.json"
+    conf.write_text(json.dumps(plain.TINY_A))
+    cmd = [sys.executable, "-m", "edgerag_b200", "--random-weights", "3", "--config", str(conf), "--save-model",
+           str(tmp_path / "rw"), "--dtype", "bf16", "--num-blocks", "16", "--max-new-tokens", "4", "--prompt-ids", "1,2,3", "--json"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=str(helpers.ROOT))
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    assert (tmp_path / "rw" / "model.safetensors").is_file()
+    assert len(json.loads(proc.stdout.strip().splitlines()[-1])["outputs"][0]["token_ids"]) == 4

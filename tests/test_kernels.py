@@ -1,0 +1,341 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch computation of the same operation,
+at sizes other than the tiny models' (odd widths, head sizes 48/80, shuffled pages, windows)."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def k():
+    from edgerag_b200.ops import kernels
+
+    return kernels
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (scale * torch.randn(shape, generator=g)).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_rows(k, dtype):
+    table, embeds = rand((301, 72), dtype, 0), rand((4, 72), dtype, 1)
+    ids = torch.tensor([5, 300, 0, 17, 9, 2], dtype=torch.int32).cuda()
+    erow = torch.tensor([-1, -1, 2, -1, 0, 3], dtype=torch.int32).cuda()
+    hidden = torch.full((6, 72), float("nan"), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.embed_rows(hidden, table, ids, status, embeds=embeds, embed_row=erow)
+    want = table[ids.long()].float()
+    want[2], want[4], want[5] = embeds[2].float(), embeds[0].float(), embeds[3].float()
+    assert torch.equal(hidden, want) and int(status) == 0
+    bad = torch.tensor([5, 301, 1, 1, 1, 1], dtype=torch.int32).cuda()
+    k.embed_rows(hidden, table, bad, status)
+    assert int(status) == 2 and torch.equal(hidden[1], torch.zeros(72, device="cuda"))   # flagged, nothing read
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 200, 2050])
+def test_add_rmsnorm(k, dtype, width):
+    hidden = rand((9, width), torch.float32, 2, 3.0)
+    delta = rand((9, width), dtype, 3)
+    weight = rand((width,), torch.float32, 4).add_(1.0)
+    if dtype == torch.bfloat16:
+        weight = weight.bfloat16().float()
+    eps = 3e-4
+    summed = hidden + delta.float()
+    want = plain.rms_norm(summed.to(dtype), weight.to(dtype), eps)  # the reference casts before the weight
+    if dtype == torch.bfloat16:   # the engine's residual stays float32: compare with statistics of the float32 sum
+        x = summed * torch.rsqrt(summed.pow(2).mean(-1, keepdim=True) + eps)
+        want = (weight * x.to(dtype).float()).to(dtype)
+    out = torch.empty((9, width), dtype=dtype, device="cuda")
+    h = hidden.clone()
+    k.add_rmsnorm(h, weight, out, eps, delta=delta)
+    torch.testing.assert_close(h, summed, atol=0, rtol=0)            # the residual sum is exact float32
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+    # rows selected, nothing written back
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32).cuda()
+    out2 = torch.empty((3, width), dtype=dtype, device="cuda")
+    h2 = hidden.clone()
+    k.add_rmsnorm(h2, weight, out2, eps, delta=delta, rows=rows, write_back=False)
+    assert torch.equal(h2, hidden) and torch.equal(out2, out[rows.long()])
+    # no delta
+    k.add_rmsnorm(h2, weight, out, eps)
+    ref = plain.rms_norm(hidden, weight, eps)
+    torch.testing.assert_close(out.float(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rot", [48, 32])
+def test_rope_cache_write(k, dtype, rot):
+    nq, nkv, d, ps, n_pages = 6, 3, 48, 8, 7
+    n = 11
+    qkv = rand((n, (nq + 2 * nkv) * d), dtype, 5)
+    positions = torch.tensor([0, 1, 2, 7000, 7001, 35, 36, 37, 38, 39, 8191], dtype=torch.int32).cuda()
+    slots = torch.tensor([3, 4, 5, 55, 8, -1, 17, 16, 30, 31, 0], dtype=torch.int32).cuda()
+    theta = 50000.0
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))).cuda()
+    kp = torch.full((n_pages, nkv, ps, d), float("nan"), dtype=dtype, device="cuda")
+    vp = torch.full_like(kp, float("nan"))
+    before = qkv.clone()
+    k.rope_cache_write(qkv, positions, inv_freq, nq, nkv, d, rot, slots=slots, k_pages=kp, v_pages=vp, page_size=ps)
+
+    x = before.float().view(n, nq + 2 * nkv, d)
+    cos, sin = plain.rope_tables(positions.cpu(), rot, theta)
+    cos, sin = cos.cuda()[:, None], sin.cuda()[:, None]
+    rotated = x[:, : nq + nkv].clone()
+    part = rotated[..., :rot]
+    rotated[..., :rot] = part * cos + plain.rotate_half(part) * sin
+    got = qkv.float().view(n, nq + 2 * nkv, d)
+    torch.testing.assert_close(got[:, :nq], rotated[:, :nq].to(dtype).float(), **tol(dtype))
+    assert torch.equal(got[:, nq + nkv:], x[:, nq + nkv:])                       # v untouched
+    written = torch.zeros(n_pages * ps, dtype=torch.bool)
+    for t in range(n):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        page, off = divmod(s, ps)
+        written[s] = True
+        torch.testing.assert_close(kp[page, :, off].float(), rotated[t, nq:].to(dtype).float(), **tol(dtype))
+        assert torch.equal(vp[page, :, off].float(), x[t, nq + nkv:])
+    untouched = kp.float().permute(0, 2, 1, 3).reshape(n_pages * ps, -1)[~written]
+    assert torch.isnan(untouched).all()                                          # no stray write
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_and_residual_and_gather(k, dtype):
+    gu = rand((5, 2 * 300), dtype, 6, 2.0)
+    out = torch.empty((5, 300), dtype=dtype, device="cuda")
+    k.swiglu(gu, out)
+    want = torch.nn.functional.silu(gu[:, :300].float()) * gu[:, 300:].float()
+    torch.testing.assert_close(out.float(), want, **tol(dtype))
+    h = rand((5, 300), torch.float32, 7)
+    h0 = h.clone()
+    k.residual_add(h, out)
+    assert torch.equal(h, h0 + out.float())
+    rows = torch.tensor([4, 1], dtype=torch.int32).cuda()
+    dst = torch.empty((2, 300), dtype=dtype, device="cuda")
+    k.gather_cast(h, dst, rows)
+    assert torch.equal(dst, h[rows.long()].to(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", [1, 7, 130])
+def test_linear(k, dtype, m):
+    n, kk = 133, 72
+    a, w = rand((m, kk), dtype, 8), rand((n, kk), dtype, 9)
+    want = a.double() @ w.double().T
+    out32 = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    k.linear(a, w, out32)
+    torch.testing.assert_close(out32.double(), want, atol=1e-4 if dtype == torch.float32 else 2e-3, rtol=1e-5)
+    if dtype == torch.float32:
+        # true 32-bit products: a TF32 product would be off by ~1e-3 relative here
+        assert float((out32.double() - want).abs().max()) < 5e-5
+    out = torch.empty((m, n), dtype=dtype, device="cuda")
+    k.linear(a, w, out)
+    torch.testing.assert_close(out.float(), want.float(), **(dict(atol=1e-4, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.15, rtol=2e-2)))
+    # strided views (a slice of a wider buffer in, a slice out) and accumulation
+    wide_in = torch.zeros((m, kk + 24), dtype=dtype, device="cuda")
+    wide_in[:, 8: 8 + kk] = a
+    wide_out = torch.zeros((m, n + 8), dtype=torch.float32, device="cuda")
+    k.linear(wide_in[:, 8: 8 + kk], w, wide_out[:, :n])
+    torch.testing.assert_close(wide_out[:, :n], out32, atol=1e-5, rtol=1e-5)
+    assert float(wide_out[:, n:].abs().max()) == 0
+    k.linear(a, w, out32, accumulate=True)
+    torch.testing.assert_close(out32.double(), 2 * want, atol=2e-4 if dtype == torch.float32 else 4e-3, rtol=1e-5)
+
+
+# --- attention -------------------------------------------------------------------------------
+
+def paged_case(dtype, seed, nq, nkv, d, ps, ctx_lens, q_lens, poison=True):
+    """Random keys/values for several sequences scattered over shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    n_seqs = len(ctx_lens)
+    pages_per = [-(-c // ps) for c in ctx_lens]
+    n_pages = sum(pages_per) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kp = torch.full((n_pages, nkv, ps, d), float("nan") if poison else 0.0, dtype=dtype)
+    vp = torch.full_like(kp, float("nan") if poison else 0.0)
+    max_pages = max(pages_per)
+    tables = torch.zeros((n_seqs, max_pages), dtype=torch.int32)
+    ks, vs = [], []
+    for s, c in enumerate(ctx_lens):
+        mine = [perm.pop() for _ in range(pages_per[s])]
+        tables[s, : len(mine)] = torch.tensor(mine, dtype=torch.int32)
+        kk = torch.randn((c, nkv, d), generator=g).to(dtype)
+        vv = torch.randn((c, nkv, d), generator=g).to(dtype)
+        ks.append(kk)
+        vs.append(vv)
+        for p in range(c):
+            kp[mine[p // ps], :, p % ps] = kk[p]
+            vp[mine[p // ps], :, p % ps] = vv[p]
+    n_tok = sum(q_lens)
+    q = torch.randn((n_tok, nq * d), generator=g).to(dtype)
+    seq_of, pos = [], []
+    for s, (c, ql) in enumerate(zip(ctx_lens, q_lens)):
+        seq_of += [s] * ql
+        pos += list(range(c - ql, c))
+    return dict(q=q, kp=kp, vp=vp, tables=tables, ks=ks, vs=vs,
+                seq_of=torch.tensor(seq_of, dtype=torch.int32), pos=torch.tensor(pos, dtype=torch.int32))
+
+
+def attention_reference(case, nq, nkv, d, scale, window=0):
+    out = []
+    r = nq // nkv
+    for t in range(case["q"].shape[0]):
+        s, p = int(case["seq_of"][t]), int(case["pos"][t])
+        lo = max(0, p - window + 1) if window else 0
+        kk = case["ks"][s][lo: p + 1].double().repeat_interleave(r, dim=1)     # (keys, nq, d)
+        vv = case["vs"][s][lo: p + 1].double().repeat_interleave(r, dim=1)
+        qq = case["q"][t].double().view(nq, d)
+        scores = torch.einsum("hd,khd->hk", qq, kk) * scale
+        probs = torch.softmax(scores, dim=-1)
+        out.append(torch.einsum("hk,khd->hd", probs, vv).reshape(-1))
+    return torch.stack(out).float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,ps,window", [(6, 2, 80, 8, 0), (4, 4, 48, 16, 0), (3, 1, 16, 4, 21), (8, 2, 128, 32, 0)])
+def test_attention_rows(k, dtype, nq, nkv, d, ps, window):
+    ctx_lens, q_lens = [37, 150, 9, 64], [37, 21, 2, 1]
+    case = paged_case(dtype, 10 + d, nq, nkv, d, ps, ctx_lens, q_lens)
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    out = torch.full((dev["q"].shape[0], nq * d), float("nan"), dtype=dtype, device="cuda")
+    k.attention_rows(dev["q"], dev["kp"], dev["vp"], dev["tables"], dev["seq_of"], dev["pos"], out, nq, scale, window=window)
+    want = attention_reference(case, nq, nkv, d, scale, window)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,ps,window,split", [(6, 2, 80, 8, 0, 64), (4, 4, 64, 16, 0, 512), (3, 1, 16, 4, 100, 32), (2, 1, 256, 16, 0, 128)])
+def test_attention_decode(k, dtype, nq, nkv, d, ps, window, split):
+    ctx_lens = [1, 63, 64, 65, 700, 129]
+    q_lens = [1] * len(ctx_lens)
+    case = paged_case(dtype, 20 + d, nq, nkv, d, ps, ctx_lens, q_lens)
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    n = len(ctx_lens)
+    max_splits = max((c - 1) // split - (max(0, c - window) if window else 0) // split + 1 for c in ctx_lens)
+    acc_n, ml_n = k.decode_scratch_floats(n, nq, d, max_splits)
+    part_acc = torch.full((acc_n,), float("nan"), device="cuda")
+    part_ml = torch.full((ml_n,), float("nan"), device="cuda")
+    out = torch.full((n, nq * d), float("nan"), dtype=dtype, device="cuda")
+    token_of_seq = torch.arange(n, dtype=torch.int32).cuda()
+    k.attention_decode(dev["q"], dev["kp"], dev["vp"], dev["tables"], token_of_seq, dev["pos"], out, nq, scale,
+                       part_acc, part_ml, max_splits, window=window, split_keys=split)
+    want = attention_reference(case, nq, nkv, d, scale, window)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+    # the row kernel gives the same answer for the same tokens
+    out2 = torch.empty_like(out)
+    k.attention_rows(dev["q"], dev["kp"], dev["vp"], dev["tables"], dev["seq_of"], dev["pos"], out2, nq, scale, window=window)
+    torch.testing.assert_close(out2.float(), out.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(k, dtype):
+    """One key far back, in the first page, gets a score that stands out: the output must be its value.
+    A kernel that drops a page, mis-walks the block table or masks too much cannot pass."""
+    nq, nkv, d, ps = 4, 2, 64, 16
+    ctx = 900
+    case = paged_case(dtype, 77, nq, nkv, d, ps, [ctx, ctx], [1, 5])
+    far = {0: 3, 1: 17}
+    for s in (0, 1):
+        page, off = int(case["tables"][s, far[s] // ps]), far[s] % ps
+        for h in range(nkv):
+            key = torch.zeros(d)
+            key[5 + h] = 12.0
+            case["ks"][s][far[s], h] = key.to(dtype)
+            case["kp"][page, h, off] = key.to(dtype)
+    q = torch.zeros((6, nq, d))
+    for h in range(nq):
+        q[:, h, 5 + h // 2] = 12.0          # q.k_far * scale = 144 / 8 = 18; every other score is ~N(0, 1.5^2)
+    case["q"] = q.view(6, -1).to(dtype)
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    out = torch.empty((6, nq * d), dtype=dtype, device="cuda")
+    k.attention_rows(dev["q"], dev["kp"], dev["vp"], dev["tables"], dev["seq_of"], dev["pos"], out, nq, scale)
+    want = attention_reference(case, nq, nkv, d, scale)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+    for t in range(6):
+        s = int(case["seq_of"][t])
+        v_far = case["vs"][s][far[s]].float().repeat_interleave(2, dim=0).reshape(-1)
+        assert float((out[t].float().cpu() - v_far).abs().max()) < 0.02 + (0.02 if dtype == torch.bfloat16 else 0)
+    acc_n, ml_n = k.decode_scratch_floats(1, nq, d, 8)
+    out_d = torch.empty((1, nq * d), dtype=dtype, device="cuda")
+    k.attention_decode(dev["q"][:1], dev["kp"], dev["vp"], dev["tables"], torch.zeros(1, dtype=torch.int32).cuda(),
+                       dev["pos"], out_d, nq, scale, torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda"),
+                       8, split_keys=128)
+    torch.testing.assert_close(out_d.float().cpu(), want[:1], **tol(dtype))
+
+
+def test_attention_refuses_bad_head_sizes(k):
+    from edgerag_b200.ops.kernels import KernelError
+
+    q = torch.zeros((1, 2 * 24), device="cuda")
+    kp = torch.zeros((1, 2, 4, 24), device="cuda")
+    t = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(KernelError, match="head_dim 24"):
+        k.attention_rows(q, kp, kp, t, z, z, torch.empty_like(q), 2, 1.0)
+
+
+# --- sampling --------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("vocab", [1000, 49155])
+def test_greedy_takes_the_first_maximum(k, vocab):
+    logits = rand((5, vocab + 5), torch.float32, 30)[:, :vocab]        # a row-strided view, as the engine's
+    logits[1, 77] = logits[1, 900] = 50.0                               # a tie: the first index wins
+    logits[2, vocab - 1] = 60.0
+    logits[3, 0] = 60.0
+    tokens = torch.full((5,), -1, dtype=torch.int32, device="cuda")
+    k.sample_rows(logits, tokens)
+    want = [int(logits[i].argmax()) for i in range(5)]
+    want[1] = 77
+    assert tokens.tolist() == want
+
+
+def test_temperature_sampling_follows_the_distribution(k):
+    vocab, rows, temp = 1000, 4096, 0.7
+    base = rand((1, vocab), torch.float32, 31, 2.0)
+    logits = base.expand(rows, vocab).contiguous()
+    states = torch.arange(rows, dtype=torch.int64).mul_(0x9E3779B97F4A7C15 % (1 << 62)).cuda()
+    temps = torch.full((rows,), temp, device="cuda")
+    temps[:3] = 0.0                                                     # greedy rows in the same launch
+    tokens = torch.empty(rows, dtype=torch.int32, device="cuda")
+    k.sample_rows(logits, tokens, temps, states)
+    probs = plain.temperature_probs(base[0].cpu(), temp)
+    cdf = torch.cumsum(probs, 0).numpy()
+    got = tokens.cpu().numpy()
+    assert (got[:3] == int(base.argmax())).all()
+    # every draw sits where the inverse CDF of its own uniform puts it (up to float32 rounding of the sums)
+    for r in range(3, rows, 7):
+        u = k.uniform_from_state(int(states[r]))
+        t = int(got[r])
+        lo = cdf[t - 1] if t else 0.0
+        assert lo - 1e-5 <= u < cdf[t] + 1e-5, (r, u, t, lo, cdf[t])
+    # and the draws as a whole follow the distribution
+    counts = np.bincount(got[3:], minlength=vocab)
+    top = np.argsort(-probs.numpy())[:20]
+    n = rows - 3
+    for t in top:
+        p = float(probs[t])
+        assert abs(counts[t] / n - p) < 5 * math.sqrt(p * (1 - p) / n) + 1e-3
+    # same state, same token; a different state changes some tokens
+    again = torch.empty_like(tokens)
+    k.sample_rows(logits, again, temps, states)
+    assert torch.equal(again, tokens)
