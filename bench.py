@@ -1,0 +1,405 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, as one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of the SmolVLM-2.2B decoder (24 layers, hidden 2048, 32 query
+and 32 key/value heads of 64, intermediate 8192, vocabulary 49155, rope theta 273768, eps 1e-5,
+tied head), random bfloat16 weights, cache pages of 16 tokens, a batch of 8 requests and a context
+of 8192 tokens.  A "step" is one decode step of the whole batch.
+
+* ``value``: decoded tokens per second, timed on the device with CUDA events around K steps of the
+  step function plus the sampling kernel, fed from the host with fixed token ids.
+* ``e2e``: the same through the Python entry point (``Engine.step``): host token ids in, sampled
+  token ids out, every step, timed by the wall clock between two synchronisations.
+* ``prefill``: one step with a portion of 2,048 prompt tokens.
+* ``roofline``: bytes the decode step has to read (every weight once, the cache of the live
+  requests) over its time, against the measured copy bandwidth.
+* ``points``: decode throughput at batch 1 and 64 with the same context.
+
+The step's inputs (3.4 GB of weights, 12.9 GB of cache at batch 8) are far larger than the 126 MB
+L2, so no flush is needed between timed iterations.  ``--impl reference`` runs the unmodified
+reference package installed under ``baseline/_ref`` through its own scheduler and executor.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+
+CONFIG_2B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 24, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 32, "head_dim": 64, "intermediate_size": 8192,
+    "vocab_size": 49155, "rope_theta": 273768.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 8192, "hidden_act": "silu", "pad_token_id": 0,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            out = {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"])}
+            if raw.get("bf16_tflops_sustained"):
+                out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+            return out, "measured"
+        except (KeyError, ValueError, json.JSONDecodeError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Reads SM clocks and throttle reasons through NVML while a timed region runs (reads only)."""
+
+    REASONS = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+               0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+               0x100: "display_clock_setting"}
+
+    def __init__(self, index: int = 0, period: float = 0.05) -> None:
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._period = period
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:  # no NVML: the record says so
+            self._nv = None
+
+    def _loop(self) -> None:
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self._period)
+
+    def __enter__(self) -> "ClockSampler":
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def merge(self, other: "ClockSampler") -> None:
+        self.samples += other.samples
+        self.reasons |= other.reasons
+
+    def record(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml_unavailable"]}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def model_numbers(cfg: dict, n_layers: int) -> dict:
+    h, d = cfg["hidden_size"], cfg["head_dim"]
+    nq, nkv, inter, vocab = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"], cfg["vocab_size"]
+    per_layer = h * d * (nq + 2 * nkv) + nq * d * h + 3 * h * inter
+    return {
+        "linear_params": n_layers * per_layer,
+        "head_params": vocab * h,
+        "norm_params": (2 * n_layers + 1) * h,
+        "kv_bytes_per_token": 2 * n_layers * nkv * d * 2,
+        "attn_flops_per_pair": 4 * nq * d * n_layers,     # q.k and p.v, per (query, visible key)
+    }
+
+
+def decode_bytes(nums: dict, context_lens: list[int]) -> float:
+    """Bytes one decode step must read: every weight once (bf16; norm weights float32) and the live cache."""
+    weights = 2 * (nums["linear_params"] + nums["head_params"]) + 4 * nums["norm_params"]
+    return weights + nums["kv_bytes_per_token"] * float(sum(context_lens))
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    sys.path.insert(0, str(ROOT))
+    from edgerag_b200.engine.engine import Engine, EngineOptions
+    from edgerag_b200.engine.step import StepEntry
+    from edgerag_b200.ops import kernels
+    from edgerag_b200.sampling.params import SamplingParams
+
+    torch.cuda.set_device(0)
+    cfg = dict(CONFIG_2B)
+    cfg["num_hidden_layers"] = args.layers
+    context, batch, block = args.context, args.batch, 16
+    nums = model_numbers(cfg, args.layers)
+    peak, peak_source = peaks()
+    point_batches = [] if args.no_points else [1, 64]
+    most = max([batch] + point_batches)
+    pages_per_seq = context // block + 2
+    engine = Engine.from_config(cfg, weights_seed=0, std=0.02, options=EngineOptions(
+        dtype="bfloat16", device="cuda:0", block_size=block, num_blocks=most * pages_per_seq + 8 + 2048 // block,
+        max_batch_size=most + 1, chunk_size=2048, max_prefills_per_step=batch, max_step_tokens=2048 * batch + most,
+        max_model_len=context + 8))
+    runner, cache = engine.runner, engine.cache
+    vocab = cfg["vocab_size"]
+    gen = torch.Generator().manual_seed(0)
+    clocks = ClockSampler()
+
+    def timed_decode(entries_fn, steps: int, warmup: int) -> tuple[float, int]:
+        """K decode steps of the step function plus sampling, on the device clock.  Returns (ms/step, own launches)."""
+        tokens = torch.empty(256, dtype=torch.int32, device="cuda")
+        for _ in range(warmup):
+            kernels.sample_rows(runner.step(entries_fn()), tokens)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = kernels.launch_counts["own"]
+        sampler = ClockSampler()
+        with sampler:
+            start.record()
+            for _ in range(steps):
+                kernels.sample_rows(runner.step(entries_fn()), tokens)
+            stop.record()
+            torch.cuda.synchronize()
+        clocks.merge(sampler)
+        return start.elapsed_time(stop) / steps, kernels.launch_counts["own"] - before
+
+    # --- prefill: one step with 2,048 prompt tokens -------------------------------------------------
+    prefill_tokens = 2048
+    ids = torch.randint(0, vocab, (prefill_tokens,), generator=gen).tolist()
+    times = []
+    for i in range(4):
+        runner.admit(f"p{i}")
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        runner.step([StepEntry(f"p{i}", tokens=ids, want=[prefill_tokens - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        runner.release(f"p{i}")
+    prefill_ms = min(times[1:])
+    pairs = prefill_tokens * (prefill_tokens + 1) / 2
+    prefill_flops = 2.0 * prefill_tokens * nums["linear_params"] + 2.0 * nums["head_params"] + nums["attn_flops_per_pair"] * pairs
+    prefill = {"value": round(prefill_tokens / (prefill_ms / 1e3), 1), "tokens": prefill_tokens, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
+               "tflop": round(prefill_flops / 1e12, 3)}
+
+    # --- the headline: batch 8 at the full context, through the entry point --------------------------
+    k, w = args.steps, args.warmup
+    prompt_len = context - (2 * (k + w) + 4)
+    for i in range(batch):
+        engine.add_request(torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(),
+                           SamplingParams(max_new_tokens=2 * (k + w) + 4), request_id=f"d{i}")
+    while any(engine.request(f"d{i}").pending > 1 or engine.request(f"d{i}").num_computed == 0 for i in range(batch)):
+        engine.step()
+    for _ in range(w):
+        engine.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    h2d = d2h = 0
+    with sampler:
+        t0 = time.perf_counter()
+        for _ in range(k):
+            events = engine.step()
+            h2d += runner.h2d_bytes_last
+            d2h += engine.d2h_bytes_last
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+    clocks.merge(sampler)
+    if len(events) != batch:
+        raise RuntimeError(f"{len(events)} of {batch} requests were decoding in the timed steps")
+    e2e = {"value": round(batch * k / e2e_s, 1), "unit": "tokens/s", "ms_per_step": round(1e3 * e2e_s / k, 4),
+           "h2d_bytes_per_step": h2d // k, "d2h_bytes_per_step": d2h // k}
+
+    # the same requests, driven below the scheduler with fixed ids, on the device clock
+    live = [f"d{i}" for i in range(batch)]
+    fixed = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+    ms_per_step, launches = timed_decode(lambda: [StepEntry(r, tokens=[t], want=[0]) for r, t in zip(live, fixed)], k, w)
+    ctx_lens = [cache.requests[r].num_tokens for r in live]
+    need = decode_bytes(nums, ctx_lens)
+    achieved = need / (ms_per_step / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peak["hbm_gbs"], 4), "bytes_per_step": int(need)}
+    value = batch / (ms_per_step / 1e3)
+    for r in live:
+        engine.scheduler.abort(engine.request(r), "bench_done")
+
+    # --- points: batch 1 and 64 at the same context (cache filled without running the prompts) --------
+    points = {}
+    for pb in point_batches:
+        names = [f"b{pb}_{i}" for i in range(pb)]
+        for r in names:
+            runner.admit(r)
+            cache.grow(r, context - 2 * (k + w) - 4)
+            cache.advance(r, context - 2 * (k + w) - 4)
+        for pool in engine.pools.kv:
+            pass  # pages keep what earlier requests wrote: finite bfloat16 values either way
+        toks = torch.randint(0, vocab, (pb,), generator=gen).tolist()
+        ms, _ = timed_decode(lambda: [StepEntry(r, tokens=[t], want=[0]) for r, t in zip(names, toks)], k, w)
+        points[f"decode_b{pb}"] = round(pb / (ms / 1e3), 1)
+        points[f"decode_b{pb}_ms"] = round(ms, 4)
+        lens = [cache.requests[r].num_tokens for r in names]
+        points[f"decode_b{pb}_hbm_frac"] = round(decode_bytes(nums, lens) / (ms / 1e3) / 1e9 / peak["hbm_gbs"], 4)
+        for r in names:
+            runner.release(r)
+
+    return {
+        "metric": "decode_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": k,
+        "warmup": w, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": "SmolVLM-2.2B decoder (random weights)", "global_batch": batch, "seq_len": context,
+            "parallelism": "single", "layers": args.layers, "layers_full": CONFIG_2B["num_hidden_layers"],
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
+            "rope_theta": cfg["rope_theta"], "rms_eps": cfg["rms_norm_eps"], "tied": True, "page_tokens": block,
+            "l2": "inputs larger than L2 (weights 3.4 GB + cache), no flush", "points_context": context,
+            "peaks": peak_source, "cuda_graphs": bool(engine.options.cuda_graphs and runner.graphs_enabled),
+        },
+        "clocks": clocks.record(), "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill,
+        "roofline": roofline, "points": points,
+    }
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference: its decoder, paged cache, scheduler and executor, random weights, float16."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "edgerag").is_dir():
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --no-deps --target baseline/_ref)"}
+    sys.path.insert(0, str(ref))
+    try:
+        import torch
+        from edgerag.cache.allocator import BlockAllocator
+        from edgerag.core.model import EdgeRagDecoder
+        from edgerag.core.spec import ModelSpec
+        from edgerag.sched.request import Request, RequestState
+        from edgerag.sched.scheduler import Scheduler, SchedulerConfig
+        from edgerag.serve.executor import ModelExecutor
+    except Exception as exc:  # the package does not import here
+        return {"impl": "reference", "unavailable": f"reference import failed: {type(exc).__name__}: {exc}"[:200]}
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+
+    c = CONFIG_2B
+    context, batch, block = args.context, args.batch, 16
+    k, w = args.steps, args.warmup
+    device = torch.device("cuda:0")
+    spec = ModelSpec(
+        model_id="bench-2.2b", model_type="smolvlm", n_layers=args.layers, hidden_size=c["hidden_size"],
+        n_q_heads=c["num_attention_heads"], n_kv_heads=c["num_key_value_heads"], head_dim=c["head_dim"],
+        vocab_size=c["vocab_size"], max_position_embeddings=context, rope_theta=c["rope_theta"], vision_layers=1,
+        vision_hidden=8, vision_image_size=16, vision_patch_size=8, scale_factor=1, image_token_id=1, pad_token_id=0,
+        rms_norm_eps=c["rms_norm_eps"], intermediate_size=c["intermediate_size"], hidden_act="silu")
+    torch.manual_seed(0)
+    with torch.device(device):
+        decoder = EdgeRagDecoder(spec).eval().to(torch.float16)
+    for p in decoder.parameters():
+        if p.dim() > 1:
+            p.data.normal_(0.0, 0.02)
+    allocator = BlockAllocator(batch * (context // block + 2) + 8, block)
+    executor = ModelExecutor(decoder, spec, allocator, device, torch.float16, chunk_size=512)
+    scheduler = Scheduler(allocator, SchedulerConfig(max_batch_size=batch, prefill_chunk_size=512,
+                                                     cow_reserve_blocks=4, max_prefills_per_step=1))
+    gen = torch.Generator().manual_seed(0)
+    new_tokens = k + w + 2
+    prompt_len = context - (2 * (k + w) + 4)
+    requests = [Request(request_id=f"d{i}", prompt_token_ids=torch.randint(0, c["vocab_size"], (prompt_len,), generator=gen).tolist(),
+                        max_new_tokens=new_tokens) for i in range(batch)]
+    for r in requests:
+        scheduler.add_request(r)
+
+    def one_step() -> int:
+        b = scheduler.schedule()
+        out = executor.execute(b)
+        made = 0
+        for r in b.requests:
+            n = out.prefilled.get(r.request_id, 0)
+            if n:
+                scheduler.on_prefill_chunk(r, n)
+            t = out.tokens.get(r.request_id)
+            if t is not None:
+                scheduler.on_token(r, t)
+                made += 1
+        scheduler.end_step()
+        return made
+
+    while not all(r.state is RequestState.DECODING for r in requests):
+        one_step()
+    for _ in range(w):
+        one_step()
+    torch.cuda.synchronize()
+    clocks = ClockSampler()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with clocks:
+        t0 = time.perf_counter()
+        start.record()
+        made = 0
+        for _ in range(k):
+            made += one_step()
+        stop.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+    ms = start.elapsed_time(stop) / k
+    nums = model_numbers(c, args.layers)
+    peak, peak_source = peaks()
+    need = decode_bytes(nums, [context - k - w] * batch)
+    achieved = need / (ms / 1e3) / 1e9
+    return {
+        "metric": "decode_tokens_per_s", "value": round(made / (ms * k / 1e3), 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": k, "warmup": w, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16", "data": "synthetic", "impl": "reference",
+        "config": {"model": "SmolVLM-2.2B decoder (random weights)", "global_batch": batch, "seq_len": context,
+                   "parallelism": "single", "layers": args.layers, "layers_full": c["num_hidden_layers"],
+                   "page_tokens": block, "path": "edgerag Scheduler + ModelExecutor (one request at a time)",
+                   "peaks": peak_source},
+        "clocks": clocks.record(),
+        "e2e": {"value": round(made / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
+        "gpu_launches": 0,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=CONFIG_2B["max_position_embeddings"])
+    ap.add_argument("--layers", type=int, default=CONFIG_2B["num_hidden_layers"],
+                    help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (nothing here uses more than one GPU)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -131,6 +131,7 @@ class ModelRunner:
         self._meta_turn = 0
         self.steps_run = 0
         self.h2d_bytes_last = 0
+        self.graphs_enabled = False
 
     # --- metadata buffer --------------------------------------------------------------------------
 
@@ -271,13 +272,14 @@ class ModelRunner:
         """Count the step's tokens as written and hand back what windows have passed."""
         for e in ordered:
             self.cache.advance(e.request_id, e.n_tokens)
-        self.pools.poison_pages(self.cache.drain_freed())
 
     @torch.inference_mode()
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Run one batch.  Returns float32 logits ``[wanted, vocab]`` (a view of a buffer that the
         next step overwrites), or ``None`` when nothing was wanted."""
         self.pools.zero_slots(self.cache.drain_new_slots())
+        # pages given back since the last step are overwritten before any of them is handed out again
+        self.pools.poison_pages(self.cache.drain_freed())
         ctx, ordered = self.prepare(entries)
         logits = self.model.forward(ctx)
         self.finish(ordered)
@@ -296,4 +298,3 @@ class ModelRunner:
 
     def release(self, request_id: object) -> None:
         self.cache.release(request_id)
-        self.pools.poison_pages(self.cache.drain_freed())

@@ -43,6 +43,10 @@ _SIGNATURES = {
 
 _functions: dict[tuple[str, str | None, str], object] = {}
 
+#: launches issued through this module: this package's own kernels, and library products
+launch_counts = {"own": 0, "library": 0}
+_LAUNCHES = {"erb_attention_decode": 2, "erb_linear": 0}
+
 
 def _fn(library: str, elem: str | None, name: str):
     key = (library, elem, name)
@@ -53,12 +57,17 @@ def _fn(library: str, elem: str | None, name: str):
         fn.argtypes = _SIGNATURES[name]
         fn.restype = c_int
         fn._erb_lib = lib
+        fn._erb_own = _LAUNCHES.get(name, 1)
         _functions[key] = fn
     return fn
 
 
 def _call(fn, *args) -> None:
     rc = fn(*args)
+    if fn._erb_own:
+        launch_counts["own"] += fn._erb_own
+    else:
+        launch_counts["library"] += 1
     if rc != 0:
         raise KernelError(fn._erb_lib.erb_last_error().decode())
 
