@@ -12,6 +12,8 @@
 // Both kernels give every thread its own keys and its own online-softmax state (running max,
 // denominator, float accumulator of D values), so the inner loop has no cross-thread traffic;
 // states are merged once at the end, in a fixed order.
+#include <mutex>
+
 #include "common.cuh"
 
 using namespace erb;
@@ -358,4 +360,66 @@ ERB_EXPORT int erb_attention_decode(const void* q, int q_row_stride, const void*
                  positions, out, out_row_stride, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size,
                  window, split_keys, scale, s)
   return fail(ERB_ERR_UNSUPPORTED, "attention_decode: head_dim %d", head_dim);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The variant for callers that cannot allocate: scratch in a file-scope device array.
+// See attention_noalloc.h for the contract.
+// ---------------------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_static_decode_scratch[ERB_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of the array on each device; looked up once per device by the first call there.
+// In host code the array's name is only a handle for the runtime, not a device pointer.
+float* g_static_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_static: device %d", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_addr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_decode_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(ERB_ERR_CUDA, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return ERB_OK;
+}
+}  // namespace
+
+ERB_EXPORT long long erb_attention_decode_static_floats(int n_seqs, int nq, int head_dim, int max_splits) {
+  return (long long)n_seqs * nq * max_splits * (head_dim + 2);
+}
+
+ERB_EXPORT int erb_attention_decode_static(const void* q, int q_row_stride, const void* k_pages,
+                                           const void* v_pages, const int* block_tables, int max_pages,
+                                           const int* token_of_seq, const int* positions, void* out,
+                                           int out_row_stride, int max_splits, int n_seqs, int nq, int nkv,
+                                           int head_dim, int page_size, int window, int split_keys,
+                                           float scale, void* stream) {
+  if (n_seqs <= 0) return ERB_OK;
+  if (max_splits <= 0 || nq <= 0 || head_dim <= 0)
+    return fail(ERB_ERR_ARG, "attention_decode_static: bad sizes");
+  const long long need = erb_attention_decode_static_floats(n_seqs, nq, head_dim, max_splits);
+  if (need > (long long)ERB_STATIC_SCRATCH_FLOATS)
+    return fail(ERB_ERR_UNSUPPORTED,
+                "attention_decode_static: %lld floats of scratch needed (sequences %d x heads %d x splits %d x "
+                "(head_dim %d + 2)), the built-in array holds %d; use erb_attention_decode with caller scratch",
+                need, n_seqs, nq, max_splits, head_dim, (int)ERB_STATIC_SCRATCH_FLOATS);
+  float* base = nullptr;
+  int rc = static_scratch_for_current_device(&base);
+  if (rc) return rc;
+  float* part_acc = base;
+  float* part_ml = base + (size_t)n_seqs * nq * max_splits * head_dim;
+  return erb_attention_decode(q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
+                              positions, out, out_row_stride, part_acc, part_ml, max_splits, n_seqs, nq, nkv,
+                              head_dim, page_size, window, split_keys, scale, stream);
 }

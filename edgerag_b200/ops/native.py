@@ -83,7 +83,7 @@ def _lib_names(library: str, elem: str | None) -> tuple[str, list[str]]:
 def _fingerprint(library: str, defines: list[str]) -> str:
     source, link, _ = LIBRARIES[library]
     h = hashlib.sha256()
-    for path in sorted(CSRC.glob("*.cuh")) + [CSRC / source]:
+    for path in sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [CSRC / source]:
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(" ".join((*NVCC_FLAGS, *defines, *link)).encode())
