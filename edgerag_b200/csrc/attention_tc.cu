@@ -1,0 +1,657 @@
+// Causal attention for portions of prompts on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// bfloat16, head size 64, queries of one (sequence, query head) in tiles of 128 rows, keys and
+// values read straight from cache pages in tiles of 128 keys.
+//
+//   S = Q K^T      tcgen05.mma  M=128 N=128 K=16 x4   A = Q tile, B = K tile, both K-major in
+//                  shared memory (rows of 128 bytes, 128-byte swizzle), accumulator in TMEM
+//   softmax        each of the 128 threads owns one query row: tcgen05.ld of its S row, running
+//                  max / denominator in float, P rounded to bfloat16 and written to shared memory
+//   O += P V       tcgen05.mma  M=128 N=64 K=16 x8    A = P (K-major), B = V tile as stored in the
+//                  cache (rows = keys, 64 contiguous values: the MN-major operand form)
+//
+// K and V tiles are brought in with cp.async 16-byte copies (zero-filled past the last visible
+// key), double buffered: tile j+1 is in flight while tile j is multiplied.  One block is 128
+// threads and 113 KB of shared memory, so two blocks share an SM and overlap each other's
+// copy, multiply and softmax phases; each allocates 256 TMEM columns.
+//
+// Every wait on an mbarrier is bounded: on a timeout the block records an error in *status,
+// skips the rest of its work, frees its TMEM and returns.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#undef ERB_ELEM
+#define ERB_ELEM 1
+#include "common.cuh"
+
+using namespace erb;
+
+ERB_DEFINE_LAST_ERROR(erb_last_error)
+
+namespace {
+
+constexpr int BM = 128;       // query rows per block
+constexpr int BN = 128;       // keys per tile
+constexpr int HD = 64;        // head size
+constexpr int kThreads = 128;
+constexpr uint32_t kTileBytes = BN * HD * 2;        // 16 KB: one K or V tile, or the Q tile
+constexpr uint32_t kPBytes = BM * BN * 2;           // 32 KB: P, two 64-key halves of 16 KB
+constexpr uint32_t kSmemBytes = kTileBytes /*Q*/ + 4 * kTileBytes /*K,V x2*/ + kPBytes + 1024 /*align*/ + 64;
+constexpr uint32_t kTmemCols = 256;                 // S: columns 0..127, P*V: columns 128..191
+constexpr uint32_t kSpinLimit = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// Byte offset of 16-byte chunk `c` (0..7) of row `r` in a tile of 128-byte rows with the
+// 128-byte swizzle: groups of 8 rows take 1024 bytes, the chunk index is XORed with the row.
+__device__ __forceinline__ uint32_t swz(int r, int c) {
+  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
+
+// Shared-memory matrix descriptor: 128-byte swizzle, 1024 bytes between groups of 8 rows.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                           // leading byte offset (unused with this swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                           // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                           // layout: 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptors: float accumulate, bfloat16 operands, M = 128.
+constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+constexpr uint32_t kIdescO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /*B is MN-major*/ |
+                             ((HD >> 3) << 17) | ((BM >> 4) << 24);
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;  // 0 bytes read: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Waits for the phase with the given parity; gives up after kSpinLimit polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(kThreads)
+attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
+                            const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                            const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
+                            const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, int out_row_stride,
+                            int n_seqs, int nq, int nkv, int page_size, float scale_log2, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t sQ = base, sK0 = base + kTileBytes, sV0 = sK0 + 2 * kTileBytes, sP = sV0 + 2 * kTileBytes;
+  const uint32_t bar_s = sP + kPBytes, bar_o = bar_s + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_s - base) + 16);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int h = blockIdx.y;
+  const int kvh = h / (nq / nkv);
+
+  // Which sequence and which 128-row tile of it this block owns.
+  int tile = blockIdx.x, seq = -1, q0 = 0, rows = 0;
+  for (int s = 0; s < n_seqs; ++s) {
+    const int begin = seq_starts[s], len = seq_starts[s + 1] - begin;
+    const int n_tiles = (len + BM - 1) / BM;
+    if (tile < n_tiles) { seq = s; q0 = begin + tile * BM; rows = min(BM, len - tile * BM); break; }
+    tile -= n_tiles;
+  }
+  if (seq < 0) return;  // the grid was sized with an upper bound
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier block gave up: do not pile on
+  const int pos0 = positions[q0];
+  const int last_key = pos0 + rows - 1;
+  const int n_kv_tiles = last_key / BN + 1;
+  const int* bt = block_tables + (size_t)seq * max_pages;
+
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_o));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+
+  // Each thread copies chunk (tid % 8) of rows (tid / 8) + 16 i, so a warp covers whole 128-byte rows.
+  const int lc = tid & 7, lr = tid >> 3;
+  auto load_kv = [&](int j, int stage) {
+    const uint32_t dK = sK0 + stage * kTileBytes, dV = sV0 + stage * kTileBytes;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = lr + 16 * i;
+      const int key = j * BN + r;
+      const bool valid = key <= last_key;
+      size_t off = 0;
+      if (valid) {
+        const int page = bt[key / page_size];
+        off = (((size_t)page * nkv + kvh) * page_size + (key % page_size)) * HD + lc * 8;
+      }
+      cp_async16(dK + swz(r, lc), k_pages + off, valid);
+      cp_async16(dV + swz(r, lc), v_pages + off, valid);
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = lr + 16 * i;
+    const bool valid = r < rows;
+    const __nv_bfloat16* src = q + (size_t)(q0 + (valid ? r : 0)) * q_row_stride + (size_t)h * HD + lc * 8;
+    cp_async16(sQ + swz(r, lc), src, valid);
+  }
+  load_kv(0, 0);
+
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes of TMEM
+  const int my_pos = pos0 + tid;
+
+  float o[HD];
+#pragma unroll
+  for (int d = 0; d < HD; ++d) o[d] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  bool ok = true;
+
+  for (int j = 0; j < n_kv_tiles; ++j) {
+    const int stage = j & 1;
+    cp_async_wait_all();
+    fence_async_proxy();
+    __syncthreads();                       // tile j (and Q) are in shared memory for everyone
+    if (j + 1 < n_kv_tiles) load_kv(j + 1, stage ^ 1);
+
+    if (tid == 0 && ok) {
+      fence_after_sync();
+      const uint64_t dq = make_desc(sQ), dk = make_desc(sK0 + stage * kTileBytes);
+#pragma unroll
+      for (int k = 0; k < HD / 16; ++k) mma_bf16(tmem, dq + 2 * k, dk + 2 * k, kIdescS, k > 0);
+      mma_commit(bar_s);
+    }
+    if (ok && !mbar_wait(bar_s, j & 1)) ok = false;
+    fence_after_sync();
+
+    float alpha = 1.f;
+    if (ok) {
+      // Pass 1: the row's maximum over the visible keys of this tile.
+      const bool diag = (j * BN + BN - 1) > pos0;      // some key of the tile is masked for some row
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        float s[32];
+        tmem_ld32(t_row + c * 32, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = j * BN + c * 32 + i;
+          if (!diag || key <= my_pos) m_tile = fmaxf(m_tile, s[i]);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      const float ms = (m_new == -INFINITY) ? 0.f : m_new * scale_log2;
+      alpha = exp2f(m_run * scale_log2 - ms);           // 0 on the first tile (m_run = -inf)
+      if (m_run == -INFINITY) alpha = 0.f;
+      float l_tile = 0.f;
+      // Pass 2: probabilities, rounded to bfloat16, into the P tile (two 64-key halves).
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        float s[32];
+        tmem_ld32(t_row + c * 32, s);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int key = j * BN + c * 32 + i;
+          float p0 = (!diag || key <= my_pos) ? exp2f(s[i] * scale_log2 - ms) : 0.f;
+          float p1 = (!diag || key + 1 <= my_pos) ? exp2f(s[i + 1] * scale_log2 - ms) : 0.f;
+          l_tile += p0 + p1;
+          __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+          packed[i / 2] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        const int half = c >> 1;                       // keys 0..63 or 64..127
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (c & 1) * 4 + g;           // 16-byte chunk inside the half's 128-byte row
+          uint8_t* dst = smem + (sP - base) + half * (BM * 128) + swz(tid, chunk);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+        }
+      }
+      l_run = l_run * alpha + l_tile;
+      m_run = m_new;
+    }
+    fence_async_proxy();
+    fence_before_sync();
+    __syncthreads();                       // P is written and every thread is done reading S
+
+    if (tid == 0 && ok) {
+      fence_after_sync();
+      const uint64_t dp = make_desc(sP), dv = make_desc(sV0 + stage * kTileBytes);
+#pragma unroll
+      for (int k = 0; k < BN / 16; ++k) {
+        const uint64_t a = dp + (uint64_t)((k >> 2) * (BM * 128 >> 4) + (k & 3) * 2);   // half, then 32 bytes per step
+        const uint64_t b = dv + (uint64_t)(k * (2048 >> 4));                            // 16 keys = 2 groups of 8 rows
+        mma_bf16(tmem + BN, a, b, kIdescO, k > 0);
+      }
+      mma_commit(bar_o);
+    }
+    if (ok && !mbar_wait(bar_o, j & 1)) ok = false;
+    fence_after_sync();
+    if (ok) {
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        float pv[32];
+        tmem_ld32(t_row + BN + c * 32, pv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + pv[i];
+      }
+    }
+    fence_before_sync();
+  }
+  cp_async_wait_all();
+  __syncthreads();
+
+  if (!ok) {
+    atomicCAS(status, 0, 1000000 + (int)blockIdx.x);
+  } else if (tid < rows) {
+    const float inv = 1.f / l_run;
+    __nv_bfloat16* dst = out + (size_t)(q0 + tid) * out_row_stride + (size_t)h * HD;
+#pragma unroll
+    for (int d = 0; d < HD; d += 8) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(o[d + 2 * i] * inv, o[d + 2 * i + 1] * inv);
+        w[i] = *reinterpret_cast<uint32_t*>(&b);
+      }
+      *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (warp == 0) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+}  // namespace
+
+// Portions of prompts only (bfloat16, head_dim 64, no window).  q / out: row t is token t of the
+// batch; seq_starts: int32 [n_seqs + 1] token offsets of the sequences to process (consecutive
+// rows of block_tables); n_tiles: sum over them of ceil(length / 128) (an upper bound is fine).
+// status: device int, set non-zero if a block gave up waiting on the tensor cores.
+ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
+                                        const int* block_tables, int max_pages, const int* seq_starts,
+                                        const int* positions, void* out, int out_row_stride, int n_seqs,
+                                        int n_tiles, int nq, int nkv, int head_dim, int page_size, float scale,
+                                        int* status, void* stream) {
+  if (n_seqs <= 0 || n_tiles <= 0) return ERB_OK;
+  if (head_dim != HD) return fail(ERB_ERR_UNSUPPORTED, "attention_prefill_tc: head_dim %d (this kernel takes 64)", head_dim);
+  if (nq <= 0 || nkv <= 0 || nq % nkv || nq > 65535) return fail(ERB_ERR_ARG, "attention_prefill_tc: bad head counts");
+  if (page_size <= 0 || max_pages <= 0 || !status) return fail(ERB_ERR_ARG, "attention_prefill_tc: bad cache arguments");
+  if (q_row_stride % 8 || out_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
+      ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+    return fail(ERB_ERR_UNSUPPORTED, "attention_prefill_tc: rows must be 16-byte aligned");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kSmemBytes);
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_prefill_tc: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const float scale_log2 = scale * 1.4426950408889634f;
+  attention_prefill_tc_kernel<<<dim3(n_tiles, nq), kThreads, kSmemBytes, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+      block_tables, max_pages, seq_starts, positions, (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv,
+      page_size, scale_log2, status);
+  return check_launch("attention_prefill_tc");
+}
+
+// =============================================================================================
+// Decode attention (one new token per sequence) streamed with bulk asynchronous copies.
+//
+// A block owns one (split of keys, kv head, sequence) and all query heads of that kv head's group.
+// The keys and values of its split arrive in shared memory through cp.async.bulk copies of whole
+// page segments (one contiguous run of rows per page), kStages stages deep, each stage signalled by
+// an mbarrier with a transaction count; four warps consume a stage while the next ones are in
+// flight, so the bytes in flight per SM are set by the pipeline depth, not by registers.
+// Inside a stage a key is handled by D/8 lanes (16 bytes each); the dot product is finished with
+// shuffles and every lane keeps the running max, denominator and 8 accumulators of its slice.
+// Partial results go to the same scratch layout as the general kernel; a combine kernel merges the
+// splits in order.  bfloat16, head size 32, 64 or 128.
+// =============================================================================================
+namespace {
+
+constexpr int kDecThreads = 128;
+constexpr int kStages = 4;
+constexpr int kMaxGroup = 8;          // query heads per kv head handled in one pass
+
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+template <int D, int R>   // head size; query heads per kv head (1..kMaxGroup)
+__global__ void __launch_bounds__(kDecThreads)
+attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
+                             const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                             const int* __restrict__ block_tables, int max_pages,
+                             const int* __restrict__ token_of_seq, const int* __restrict__ positions,
+                             float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
+                             int nkv, int page_size, int split_keys, float scale_log2, int* __restrict__ status) {
+  constexpr int LPK = D / 8;                 // lanes per key
+  constexpr int KPW = 32 / LPK;              // keys a warp handles per pass
+  constexpr int STAGE_KEYS = 4096 / D;       // 8 KB of keys and 8 KB of values per stage
+  constexpr int ROW = D * 2;                 // bytes per key row
+  constexpr uint32_t STAGE_BYTES = STAGE_KEYS * ROW;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 127u) & ~127u;
+  uint8_t* smem = smem_raw + (base - raw);
+  // layout: K stages | V stages | barriers | merge area
+  const uint32_t sK = base, sV = base + kStages * STAGE_BYTES, sBar = sV + kStages * STAGE_BYTES;
+  float* merge = reinterpret_cast<float*>(smem + 2 * kStages * STAGE_BYTES + 64);   // [4 warps][R][D + 2]
+
+  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t = token_of_seq[seq];
+  const int pos = positions[t];
+  const int begin = split * split_keys;
+  const int end = min(pos + 1, begin + split_keys);
+  if (begin >= end) return;
+  const int* bt = block_tables + (size_t)seq * max_pages;
+  const int n_tiles = (end - begin + STAGE_KEYS - 1) / STAGE_KEYS;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sBar + 8 * s));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](int tile) {   // thread 0 only
+    const int s = tile % kStages;
+    const int kb = begin + tile * STAGE_KEYS, ke = min(end, kb + STAGE_KEYS);
+    const uint32_t bar = sBar + 8 * s;
+    mbar_expect(bar, (uint32_t)(ke - kb) * ROW * 2);
+    int k = kb;
+    while (k < ke) {
+      const int page = bt[k / page_size], off = k % page_size;
+      const int n = min(page_size - off, ke - k);
+      const size_t src = (((size_t)page * nkv + kvh) * page_size + off) * D;
+      const uint32_t dst = (uint32_t)(s * STAGE_BYTES + (k - kb) * ROW);
+      bulk_copy(sK + dst, k_pages + src, (uint32_t)n * ROW, bar);
+      bulk_copy(sV + dst, v_pages + src, (uint32_t)n * ROW, bar);
+      k += n;
+    }
+  };
+  if (tid == 0) {
+    for (int i = 0; i < kStages && i < n_tiles; ++i) issue(i);
+  }
+
+  // This lane's slice of every query head of the group, pre-multiplied by scale * log2(e).
+  const int sub = lane / LPK, chunk = lane % LPK;
+  float qr[R][8];
+#pragma unroll
+  for (int g = 0; g < R; ++g) {
+    const __nv_bfloat16* qp = q + (size_t)t * q_row_stride + (size_t)(kvh * R + g) * D + chunk * 8;
+    float tmp[8];
+    load8(qp, tmp);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qr[g][i] = tmp[i] * scale_log2;
+  }
+  float m_run[R], l_run[R], acc[R][8];
+#pragma unroll
+  for (int g = 0; g < R; ++g) {
+    m_run[g] = -INFINITY; l_run[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
+  }
+
+  bool ok = true;
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int s = tile % kStages;
+    if (ok && !mbar_wait(sBar + 8 * s, (tile / kStages) & 1)) ok = false;
+    if (ok) {
+      const int kb = begin + tile * STAGE_KEYS;
+      const int n_here = min(end - kb, STAGE_KEYS);
+      const uint8_t* kt = smem + s * STAGE_BYTES;
+      const uint8_t* vt = smem + kStages * STAGE_BYTES + s * STAGE_BYTES;
+      // warp w takes keys w*KPW + sub, then strides by 4*KPW
+      for (int kk = warp * KPW + sub; kk < STAGE_KEYS; kk += 4 * KPW) {
+        const bool valid = kk < n_here;                     // uniform per LPK-lane group
+        float kf[8], vf[8];
+        if (valid) {
+          load8(reinterpret_cast<const __nv_bfloat16*>(kt + kk * ROW) + chunk * 8, kf);
+          load8(reinterpret_cast<const __nv_bfloat16*>(vt + kk * ROW) + chunk * 8, vf);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+        }
+#pragma unroll
+        for (int g = 0; g < R; ++g) {
+          float sc = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sc = fmaf(qr[g][i], kf[i], sc);
+#pragma unroll
+          for (int o = 1; o < LPK; o <<= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+          if (valid) {
+            float p;
+            if (sc > m_run[g]) {
+              const float a = exp2f(m_run[g] - sc);
+              l_run[g] *= a;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[g][i] *= a;
+              m_run[g] = sc;
+              p = 1.f;
+            } else {
+              p = exp2f(sc - m_run[g]);
+            }
+            l_run[g] += p;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i]);
+          }
+        }
+      }
+    }
+    __syncthreads();                                        // everyone is done with stage s
+    if (tid == 0 && ok && tile + kStages < n_tiles) issue(tile + kStages);
+  }
+
+  // Merge the KPW key groups of each warp (lanes that share `chunk`), then the four warps.
+#pragma unroll
+  for (int g = 0; g < R; ++g) {
+    float m = m_run[g];
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float f = (m_run[g] == -INFINITY) ? 0.f : exp2f(m_run[g] - m);
+    float l = l_run[g] * f;
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float a = acc[g][i] * f;
+#pragma unroll
+      for (int o = LPK; o < 32; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      acc[g][i] = a;
+    }
+    float* w = merge + (warp * R + g) * (D + 2);
+    if (sub == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[chunk * 8 + i] = acc[g][i];
+      if (chunk == 0) { w[D] = m; w[D + 1] = l; }
+    }
+  }
+  __syncthreads();
+  if (!ok) {
+    if (tid == 0) atomicCAS(status, 0, 2000000 + (int)blockIdx.x);
+    return;
+  }
+  for (int idx = tid; idx < R * D; idx += kDecThreads) {
+    const int g = idx / D, d = idx % D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[(w * R + g) * (D + 2) + D]);
+    float sum = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = merge[(w * R + g) * (D + 2) + D];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      sum += merge[(w * R + g) * (D + 2) + d] * f;
+      l += merge[(w * R + g) * (D + 2) + D + 1] * f;
+    }
+    const size_t slot = ((size_t)seq * nq + kvh * R + g) * max_splits + split;
+    part_acc[slot * D + d] = sum;
+    if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+  }
+}
+
+// Merges the splits of each (sequence, head) in order.  The partial maxima are in the log2 domain.
+__global__ void attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                                     const int* __restrict__ token_of_seq, const int* __restrict__ positions,
+                                                     __nv_bfloat16* __restrict__ out, int out_row_stride, int max_splits,
+                                                     int nq, int head_dim, int split_keys) {
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int t = token_of_seq[seq];
+  const int n_splits = positions[t] / split_keys + 1;
+  const size_t base = ((size_t)seq * nq + h) * max_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; ++s) l += part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - m);
+  const float inv = 1.f / l;
+  __nv_bfloat16* o = out + (size_t)t * out_row_stride + (size_t)h * head_dim;
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float sum = 0.f;
+    for (int s = 0; s < n_splits; ++s) sum += part_acc[(base + s) * head_dim + d] * exp2f(part_ml[(base + s) * 2] - m);
+    o[d] = __float2bfloat16_rn(sum * inv);
+  }
+}
+
+template <int D, int R>
+int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
+                       const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
+                       float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
+                       int split_keys, float scale_log2, int* status, cudaStream_t s) {
+  constexpr int STAGE_BYTES = (4096 / D) * D * 2;
+  const size_t smem = 2 * kStages * STAGE_BYTES + 64 + (size_t)4 * R * (D + 2) * sizeof(float) + 128;
+  auto kern = attention_decode_bulk_kernel<D, R>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_decode_bulk: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  kern<<<dim3(max_splits, nkv, n_seqs), kDecThreads, smem, s>>>((const __nv_bfloat16*)q, q_row_stride,
+      (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, token_of_seq, positions,
+      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, status);
+  return check_launch("attention_decode_bulk");
+}
+
+template <int D>
+int dispatch_group(int r, const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
+                   const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
+                   float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
+                   int split_keys, float scale_log2, int* status, cudaStream_t s) {
+#define ERB_R(RR)                                                                                              \
+  case RR: return launch_decode_bulk<D, RR>(q, q_row_stride, k_pages, v_pages, block_tables, max_pages,        \
+                                            token_of_seq, positions, part_acc, part_ml, max_splits, n_seqs, nq, \
+                                            nkv, page_size, split_keys, scale_log2, status, s);
+  switch (r) { ERB_R(1) ERB_R(2) ERB_R(3) ERB_R(4) ERB_R(5) ERB_R(6) ERB_R(7) ERB_R(8) }
+#undef ERB_R
+  return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: %d query heads per kv head (at most %d)", r, kMaxGroup);
+}
+
+}  // namespace
+
+// Same contract as the general decode entry point (scratch provided by the caller, splits at
+// absolute multiples of split_keys), for bfloat16 with head_dim 32 / 64 / 128, no window, at most
+// 8 query heads per kv head, and page rows that are 16-byte multiples.
+ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
+                                         const int* block_tables, int max_pages, const int* token_of_seq,
+                                         const int* positions, void* out, int out_row_stride, float* part_acc,
+                                         float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int head_dim,
+                                         int page_size, int split_keys, float scale, int* status, void* stream) {
+  if (n_seqs <= 0) return ERB_OK;
+  if (nq <= 0 || nkv <= 0 || nq % nkv) return fail(ERB_ERR_ARG, "attention_decode_bulk: bad head counts");
+  if (max_splits <= 0 || split_keys <= 0 || !part_acc || !part_ml || !status || page_size <= 0)
+    return fail(ERB_ERR_ARG, "attention_decode_bulk: bad arguments");
+  if (q_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+    return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: rows must be 16-byte aligned");
+  if (n_seqs > 65535 || nkv > 65535) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: grid too large");
+  const float scale_log2 = scale * 1.4426950408889634f;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int r = nq / nkv;
+  int rc;
+  switch (head_dim) {
+    case 32: rc = dispatch_group<32>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
+                                     positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size, split_keys,
+                                     scale_log2, status, s); break;
+    case 64: rc = dispatch_group<64>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
+                                     positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size, split_keys,
+                                     scale_log2, status, s); break;
+    case 128: rc = dispatch_group<128>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
+                                       positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size,
+                                       split_keys, scale_log2, status, s); break;
+    default: return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: head_dim %d (takes 32, 64, 128)", head_dim);
+  }
+  if (rc) return rc;
+  attention_decode_bulk_combine_kernel<<<dim3(nq, n_seqs), 64, 0, s>>>(part_acc, part_ml, token_of_seq, positions,
+      (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
+  return check_launch("attention_decode_bulk_combine");
+}

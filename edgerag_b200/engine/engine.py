@@ -122,7 +122,8 @@ class Engine:
         self.cache = CacheManager(layout, options.block_size, n_pages, max_requests=options.max_batch_size)
         self.pools = DevicePools(layout, options.block_size, n_pages, options.max_batch_size, self.dtype,
                                  self.device, poison=options.poison_freed_pages)
-        self.runner = ModelRunner(model, self.cache, self.pools, max_step_tokens=max_step)
+        self.runner = ModelRunner(model, self.cache, self.pools, max_step_tokens=max_step,
+                                  cuda_graphs=options.cuda_graphs)
         self.scheduler = Scheduler(self.cache, SchedulerConfig(
             max_batch_size=options.max_batch_size, prefill_chunk_size=options.chunk_size,
             max_prefills_per_step=options.max_prefills_per_step, max_step_tokens=max_step,
@@ -239,6 +240,7 @@ class Engine:
                 logits, [e.request.sampling for e in sampled], [e.request.seed for e in sampled],
                 [e.request.num_generated for e in sampled])
             new_tokens = {e.request.request_id: t for e, t in zip(sampled, tokens)}
+            self.runner.raise_if_flagged()       # the sampler synchronised: the status copy is current
             self.d2h_bytes_last = 4 * len(tokens)
         self.scheduler.update(batch, new_tokens)
         events = []

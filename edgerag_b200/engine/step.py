@@ -26,6 +26,9 @@ from ..cache.manager import CacheManager, OutOfPagesError
 from ..ops import kernels
 
 
+_ITEMSIZE = {torch.float32: 4, torch.bfloat16: 2, torch.int32: 4, torch.int64: 8, torch.uint8: 1, torch.float16: 2}
+
+
 class StepError(ValueError):
     """A step was asked for that cannot run (unknown request, bad ids, no room in the batch)."""
 
@@ -50,17 +53,26 @@ class Workspace:
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self._bufs: dict[str, torch.Tensor] = {}
-        self.frozen = False  # set while a CUDA graph that uses the buffers is alive
+        self._views: dict[tuple, torch.Tensor] = {}
+        #: called before a buffer that CUDA graphs may point at is replaced by a larger one
+        self.on_move = None
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
-        need = int(np.prod(shape, dtype=np.int64)) * torch.empty((), dtype=dtype).element_size()
+        key = (name, shape, dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
+        need = int(np.prod(shape, dtype=np.int64)) * _ITEMSIZE[dtype]
         buf = self._bufs.get(name)
         if buf is None or buf.numel() < need:
-            if self.frozen and buf is not None:
-                raise StepError(f"workspace buffer {name} would move while a CUDA graph uses it")
+            if buf is not None and self.on_move is not None:
+                self.on_move()
             buf = torch.empty(max(need, 256), dtype=torch.uint8, device=self.device)
             self._bufs[name] = buf
-        return buf[:need].view(dtype).view(shape)
+            self._views = {k: v for k, v in self._views.items() if k[0] != name}
+        view = buf[:need].view(dtype).view(shape)
+        self._views[key] = view
+        return view
 
     def nbytes(self) -> int:
         return sum(b.numel() for b in self._bufs.values())
@@ -78,6 +90,9 @@ class StepContext:
         self.token_ids = self.embed_row = self.positions = self.seq_of_token = None
         self.token_of_seq = self.want_rows = self.state_slots = self.seq_starts = None
         self.embeds: torch.Tensor | None = None
+        self.max_pages = 1
+        self.graph_key: tuple | None = None          # set when the step has the fixed layout of a CUDA graph
+        self.fixed_decode_splits: int | None = None
         self.slots: list[torch.Tensor] = []
         self.block_tables: list[torch.Tensor] = []
         #: host copies for parts that size launches or loop over sequences
@@ -100,8 +115,8 @@ class StepContext:
 
     def decode_splits(self, window: int, split_keys: int = kernels.DECODE_SPLIT_KEYS) -> int:
         """Largest number of key splits any single-token sequence of the batch has."""
-        if self._runner.fixed_decode_splits is not None:
-            return self._runner.fixed_decode_splits
+        if self.fixed_decode_splits is not None:   # a captured layout: the bound must hold for every replay
+            return self.fixed_decode_splits if window <= 0 else min(self.fixed_decode_splits, window // split_keys + 2)
         most = 1
         for pos in self.host_positions_last[: self.n_decode]:
             lo = max(0, pos - window + 1) if window > 0 else 0
@@ -113,7 +128,7 @@ class ModelRunner:
     """Owns the model, the cache and the scratch of one device, and runs steps on them."""
 
     def __init__(self, model, cache: CacheManager, pools: DevicePools, max_step_tokens: int,
-                 check_status: bool = False) -> None:
+                 check_status: bool = False, cuda_graphs: bool = False) -> None:
         self.model = model
         self.cache = cache
         self.pools = pools
@@ -122,8 +137,10 @@ class ModelRunner:
         self.max_step_tokens = max_step_tokens
         self.check_status = check_status
         self.workspace = Workspace(self.device)
+        self.workspace.on_move = self.drop_graphs
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.fixed_decode_splits: int | None = None
+        #: host copy of the status word, refreshed asynchronously at the end of every step
+        self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self._meta_dev: torch.Tensor | None = None
         #: pinned staging buffers, used in turn; each waits for its last upload before it is rewritten
         self._meta_host: list[torch.Tensor | None] = [None] * 4
@@ -131,7 +148,13 @@ class ModelRunner:
         self._meta_turn = 0
         self.steps_run = 0
         self.h2d_bytes_last = 0
-        self.graphs_enabled = False
+        #: decode-only steps are captured in CUDA graphs, one per (sequences, page bucket, wanted rows)
+        self.graphs_enabled = bool(cuda_graphs)
+        self._graphs: dict[tuple, tuple] = {}
+        self._graph_seen: dict[tuple, int] = {}
+        self.graph_replays = 0
+        if self.graphs_enabled:
+            self._meta_dev = torch.empty(1 << 20, dtype=torch.int32, device=self.device)
 
     # --- metadata buffer --------------------------------------------------------------------------
 
@@ -139,8 +162,7 @@ class ModelRunner:
         """Copy the step's int32 metadata to the device through pinned memory (one transfer)."""
         n = flat.size
         if self._meta_dev is None or self._meta_dev.numel() < n:
-            if self.workspace.frozen:
-                raise StepError("the metadata buffer would move while a CUDA graph uses it")
+            self.drop_graphs()
             self._meta_dev = torch.empty(max(4096, 2 * n), dtype=torch.int32, device=self.device)
         i = self._meta_turn = (self._meta_turn + 1) % len(self._meta_host)
         if self._meta_event[i] is not None:
@@ -216,6 +238,10 @@ class ModelRunner:
         for e in ordered:
             rc = self.cache.requests[e.request_id]
             max_pages = max(max_pages, max((len(t.pages) for t in rc.tables), default=1))
+        graphable = self.graphs_enabled and n_decode == n_seqs and all(e.embeds is None for e in ordered)
+        if graphable:
+            # a captured step has a fixed layout: block tables padded to a power of two of pages
+            max_pages = max(4, 1 << (max_pages - 1).bit_length())
         tables = np.zeros((n_groups, n_seqs, max_pages), np.int32)
         want_of_entry: dict[int, list[int]] = {}
         embed_chunks: list[torch.Tensor] = []
@@ -263,6 +289,10 @@ class ModelRunner:
         per = n_seqs * max_pages
         ctx.block_tables = [tables_d[g * per: (g + 1) * per].view(n_seqs, max_pages) for g in range(n_groups)]
         ctx.n_tokens, ctx.n_seqs, ctx.n_decode, ctx.n_wanted = total, n_seqs, n_decode, int(want_rows.size)
+        ctx.max_pages = max_pages
+        if graphable:
+            ctx.graph_key = (n_seqs, max_pages, int(want_rows.size))
+            ctx.fixed_decode_splits = -(-(max_pages * ps) // kernels.DECODE_SPLIT_KEYS)
         if embed_chunks:
             ctx.embeds = torch.cat([c.to(device=self.device, dtype=self.dtype, non_blocking=True)
                                     for c in embed_chunks], dim=0).contiguous()
@@ -277,18 +307,64 @@ class ModelRunner:
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Run one batch.  Returns float32 logits ``[wanted, vocab]`` (a view of a buffer that the
         next step overwrites), or ``None`` when nothing was wanted."""
+        self.raise_if_flagged()
         self.pools.zero_slots(self.cache.drain_new_slots())
         # pages given back since the last step are overwritten before any of them is handed out again
         self.pools.poison_pages(self.cache.drain_freed())
         ctx, ordered = self.prepare(entries)
-        logits = self.model.forward(ctx)
+        logits = self._forward(ctx)
         self.finish(ordered)
         self.steps_run += 1
+        self._status_host.copy_(self.status, non_blocking=True)
         if self.check_status:
-            code = int(self.status.item())
-            if code:
-                self.status.zero_()
-                raise StepError(f"a kernel flagged token {code - 1} of the batch (id or row out of range)")
+            torch.cuda.current_stream().synchronize()
+            self.raise_if_flagged()
+        return logits
+
+    def raise_if_flagged(self) -> None:
+        """Raise if a kernel of an earlier step reported a fault (checked from the pinned host copy of
+        the status word, so callers that synchronise anyway pay nothing extra)."""
+        code = int(self._status_host[0])
+        if code:
+            self.status.zero_()
+            self._status_host.zero_()
+            if code >= 1000000:
+                raise StepError(f"the tensor-core attention kernel gave up waiting (block {code - 1000000}); "
+                                "the step's results are not valid")
+            raise StepError(f"a kernel flagged token {code - 1} of the batch (id or row out of range)")
+
+    def drop_graphs(self) -> None:
+        """Forget every captured graph (a buffer they point at is about to move); they are captured again on demand."""
+        self._graphs.clear()
+        self._graph_seen.clear()
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor | None:
+        """Run the model eagerly, or replay the CUDA graph captured for this step's layout.
+
+        A layout is captured the second time it is seen (the first run sizes every scratch buffer).
+        The graph holds the kernels' arguments; what changes from step to step (ids, positions,
+        slots, block tables, wanted rows) lives in the metadata buffer at fixed offsets.
+        """
+        key = ctx.graph_key
+        if key is None:
+            return self.model.forward(ctx)
+        hit = self._graphs.get(key)
+        if hit is not None:
+            hit[0].replay()
+            self.graph_replays += 1
+            kernels.launch_counts["own"] += hit[2]
+            return hit[1]
+        seen = self._graph_seen.get(key, 0)
+        self._graph_seen[key] = seen + 1
+        logits = self.model.forward(ctx)
+        if seen >= 1:
+            graph = torch.cuda.CUDAGraph()
+            before = kernels.launch_counts["own"]
+            with torch.cuda.graph(graph):
+                captured = self.model.forward(ctx)
+            own = kernels.launch_counts["own"] - before
+            kernels.launch_counts["own"] = before       # capturing launched nothing
+            self._graphs[key] = (graph, captured, own)
         return logits
 
     # --- requests ---------------------------------------------------------------------------------

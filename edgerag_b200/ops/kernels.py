@@ -38,6 +38,9 @@ _SIGNATURES = {
     "erb_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                              c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_float, c_void_p],
+    "erb_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                 c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
@@ -277,6 +280,34 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(),
           max_splits, n_seqs, n_q_heads, nkv, d, page_size, int(window), int(split_keys), float(scale), _stream())
+
+
+def prefill_tc_supported(dtype: torch.dtype, head_dim: int, window: int) -> bool:
+    """Shapes the tensor-core prefill kernel takes; everything else goes to the general row kernel."""
+    return dtype == torch.bfloat16 and head_dim == 64 and window <= 0
+
+
+def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                         seq_starts: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_tiles: int,
+                         n_q_heads: int, scale: float, status: torch.Tensor) -> None:
+    """Causal attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64, no window).
+
+    ``qkv`` / ``out``: row t is token t of the batch (the q heads lead each qkv row);
+    ``seq_starts`` int32 ``[n + 1]``: token offsets of the n sequences to process, whose block tables
+    are the n rows of ``block_tables``; ``n_tiles``: sum of ceil(length / 128) over them.
+    """
+    _need(qkv, "qkv", torch.bfloat16, contiguous=False); _need(k_pages, "k_pages", torch.bfloat16)
+    _need(v_pages, "v_pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
+    _need(seq_starts, "seq_starts", torch.int32); _need(positions, "positions", torch.int32)
+    _need(out, "out", torch.bfloat16, contiguous=False); _need(status, "status", torch.int32)
+    _, nkv, page_size, d = k_pages.shape
+    n_seqs = seq_starts.numel() - 1
+    if qkv.stride(1) != 1 or out.stride(1) != 1 or block_tables.shape[0] < n_seqs:
+        raise KernelError("attention_prefill_tc: layout disagrees")
+    _call(_fn("attention_tc", None, "erb_attention_prefill_tc"), qkv.data_ptr(), qkv.stride(0), k_pages.data_ptr(),
+          v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_starts.data_ptr(),
+          positions.data_ptr(), out.data_ptr(), out.stride(0), n_seqs, int(n_tiles), n_q_heads, nkv, d, page_size,
+          float(scale), status.data_ptr(), _stream())
 
 
 # --- sampling --------------------------------------------------------------------------------

@@ -54,6 +54,36 @@ def test_greedy_generation_matches_plain(which, dtype, model_folders):
         assert engine2.generate(prompts, SamplingParams(max_new_tokens=16)) == outs
 
 
+def test_cuda_graph_decode_equals_eager_decode(model_folders):
+    """Decode-only steps replay a captured CUDA graph; the tokens and logits are those of the eager path."""
+    from edgerag_b200 import Engine, SamplingParams
+    from edgerag_b200.engine.step import StepEntry
+
+    folder = model_folders("b", "bfloat16", std=0.2)
+    cfg = plain.read_config(folder)
+    prompts = [helpers.random_sequence(cfg["vocab"], n, 60 + n) for n in (9, 30, 17)]
+    outs = {}
+    for graphs in (False, True):
+        engine = Engine.from_pretrained(folder, dtype="bfloat16", block_size=8, num_blocks=64, chunk_size=16,
+                                        max_batch_size=3, max_prefills_per_step=3, cuda_graphs=graphs)
+        outs[graphs] = engine.generate(prompts, SamplingParams(max_new_tokens=24))
+        assert (engine.runner.graph_replays > 10) == graphs
+    assert outs[True] == outs[False]
+    # logits of a replayed step equal those of the same step run eagerly, bit for bit
+    rows = {}
+    for graphs in (False, True):
+        engine = Engine.from_pretrained(folder, dtype="bfloat16", block_size=8, num_blocks=64, cuda_graphs=graphs)
+        r = engine.runner
+        r.admit("x"), r.admit("y")
+        r.step([StepEntry("x", tokens=prompts[0]), StepEntry("y", tokens=prompts[1])])
+        got = []
+        for i in range(12):   # crosses a page boundary and a page-count bucket on the way
+            got.append(r.step([StepEntry("x", tokens=[i + 1], want=[0]), StepEntry("y", tokens=[i + 2], want=[0])]).clone())
+        rows[graphs] = torch.stack(got)
+        assert (r.graph_replays > 0) == graphs
+    assert torch.equal(rows[True], rows[False])
+
+
 def test_prompt_embeds_temperature_and_eos(model_folders):
     from edgerag_b200 import Engine, SamplingParams
     from edgerag_b200.ops.kernels import uniform_from_state

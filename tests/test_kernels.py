@@ -283,6 +283,37 @@ def test_attention_finds_one_far_key(k, dtype):
     torch.testing.assert_close(out_d.float().cpu(), want[:1], **tol(dtype))
 
 
+@pytest.mark.parametrize("nq,nkv,ps", [(4, 2, 16), (2, 2, 8), (3, 1, 64)])
+def test_attention_prefill_tensor_cores(k, nq, nkv, ps):
+    """The tcgen05 kernel for prompt portions: whole prompts, a portion that continues from the cache
+    across a tile edge, lengths around 128 and 256, shuffled pages with NaN in every unwritten slot."""
+    d = 64
+    ctx_lens = [37, 500, 128, 129, 256, 700]
+    q_lens = [37, 300, 128, 129, 2, 257]
+    case = paged_case(torch.bfloat16, 50 + ps, nq, nkv, d, ps, ctx_lens, q_lens)
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    n_tok = dev["q"].shape[0]
+    # q as the leading columns of a wider qkv-like buffer
+    qkv = torch.zeros((n_tok, (nq + 2 * nkv) * d), dtype=torch.bfloat16, device="cuda")
+    qkv[:, : nq * d] = dev["q"]
+    starts = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32).cuda()
+    out = torch.full((n_tok, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    n_tiles = sum(-(-q // 128) for q in q_lens)
+    k.attention_prefill_tc(qkv, dev["kp"], dev["vp"], dev["tables"], starts, dev["pos"], out, n_tiles, nq, scale, status)
+    torch.cuda.synchronize()
+    assert int(status) == 0, f"the kernel gave up waiting on the tensor cores (status {int(status)})"
+    want = attention_reference(case, nq, nkv, d, scale)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+    # and it agrees with the general row kernel on the same inputs
+    out2 = torch.empty_like(out)
+    k.attention_rows(dev["q"], dev["kp"], dev["vp"], dev["tables"], dev["seq_of"], dev["pos"], out2, nq, scale)
+    torch.testing.assert_close(out.float(), out2.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_attention_refuses_bad_head_sizes(k):
     from edgerag_b200.ops.kernels import KernelError
 
