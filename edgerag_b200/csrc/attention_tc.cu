@@ -373,9 +373,11 @@ ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const v
 // =============================================================================================
 namespace {
 
-constexpr int kDecThreads = 128;
-constexpr int kStages = 4;
+constexpr int kDecThreads = 256;
+constexpr int kDecWarps = kDecThreads / 32;
+constexpr int kStages = 3;
 constexpr int kMaxGroup = 8;          // query heads per kv head handled in one pass
+constexpr int kKeysPerGroup = 4;      // keys a lane group handles per stage (independent chains)
 
 __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -385,6 +387,15 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
 __device__ __forceinline__ void mbar_expect(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// Eight bfloat16 values (one 16-byte chunk of shared memory) as floats: a shift and a mask per pair.
+__device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
 
 template <int D, int R>   // head size; query heads per kv head (1..kMaxGroup)
 __global__ void __launch_bounds__(kDecThreads)
@@ -393,22 +404,31 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
                              const int* __restrict__ block_tables, int max_pages,
                              const int* __restrict__ token_of_seq, const int* __restrict__ positions,
                              float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
-                             int nkv, int page_size, int split_keys, float scale_log2, int* __restrict__ status) {
-  constexpr int LPK = D / 8;                 // lanes per key
-  constexpr int KPW = 32 / LPK;              // keys a warp handles per pass
-  constexpr int STAGE_KEYS = 4096 / D;       // 8 KB of keys and 8 KB of values per stage
-  constexpr int ROW = D * 2;                 // bytes per key row
-  constexpr uint32_t STAGE_BYTES = STAGE_KEYS * ROW;
+                             int nkv, int page_size, int split_keys, float scale_log2, int hg,
+                             int* __restrict__ status) {
+  // hg: kv heads handled by this block.  The rows of hg neighbouring heads of one page are contiguous
+  // in the cache, so a block that takes them together copies hg * page_size rows in one piece; with
+  // small pages that is what keeps the copies long enough for the memory system.
+  constexpr int LPK = D / 8;                              // lanes per key (16 bytes each)
+  constexpr int GPW = 32 / LPK;                           // lane groups per warp
+  constexpr int STAGE_ROWS = kDecWarps * GPW * kKeysPerGroup;   // (key, head) rows per stage: 16 KB of K and of V
+  constexpr int ROW = D * 2;                              // bytes per key row
+  constexpr uint32_t STAGE_BYTES = STAGE_ROWS * ROW;
+  const int STAGE_KEYS = STAGE_ROWS / hg;                  // keys of each head per stage
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 127u) & ~127u;
   uint8_t* smem = smem_raw + (base - raw);
-  // layout: K stages | V stages | barriers | merge area
+  // layout: K stages | V stages | barriers | merge area | page ids
   const uint32_t sK = base, sV = base + kStages * STAGE_BYTES, sBar = sV + kStages * STAGE_BYTES;
-  float* merge = reinterpret_cast<float*>(smem + 2 * kStages * STAGE_BYTES + 64);   // [4 warps][R][D + 2]
+  float* merge = reinterpret_cast<float*>(smem + 2 * kStages * STAGE_BYTES + 64);   // [warps][R][D + 2]
+  int* s_pages = reinterpret_cast<int*>(merge + kDecWarps * R * (D + 2));
 
-  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int split = blockIdx.x, kvh0 = blockIdx.y * hg, seq = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warps_per_head = kDecWarps / hg;
+  const int hh = warp / warps_per_head;                    // which head of the group this warp serves
+  const int kvh = kvh0 + hh;
   const int t = token_of_seq[seq];
   const int pos = positions[t];
   const int begin = split * split_keys;
@@ -422,22 +442,42 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
     for (int s = 0; s < kStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sBar + 8 * s));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // The block table entries of the split, fetched by all threads at once: the thread that issues
+  // the copies must not wait on a global load per page.
+  const int first_page = begin / page_size;
+  const int n_pages = (end - 1) / page_size - first_page + 1;
+  for (int i = tid; i < n_pages; i += kDecThreads) s_pages[i] = bt[first_page + i];
   __syncthreads();
 
   auto issue = [&](int tile) {   // thread 0 only
     const int s = tile % kStages;
     const int kb = begin + tile * STAGE_KEYS, ke = min(end, kb + STAGE_KEYS);
     const uint32_t bar = sBar + 8 * s;
-    mbar_expect(bar, (uint32_t)(ke - kb) * ROW * 2);
-    int k = kb;
-    while (k < ke) {
-      const int page = bt[k / page_size], off = k % page_size;
-      const int n = min(page_size - off, ke - k);
-      const size_t src = (((size_t)page * nkv + kvh) * page_size + off) * D;
-      const uint32_t dst = (uint32_t)(s * STAGE_BYTES + (k - kb) * ROW);
-      bulk_copy(sK + dst, k_pages + src, (uint32_t)n * ROW, bar);
-      bulk_copy(sV + dst, v_pages + src, (uint32_t)n * ROW, bar);
-      k += n;
+    if (hg == 1) {
+      // one head: copy exactly the visible keys, one run per page
+      mbar_expect(bar, (uint32_t)(ke - kb) * ROW * 2);
+      int k = kb;
+      while (k < ke) {
+        const int page = s_pages[k / page_size - first_page], off = k % page_size;
+        const int n = min(page_size - off, ke - k);
+        const size_t src = (((size_t)page * nkv + kvh0) * page_size + off) * D;
+        const uint32_t dst = (uint32_t)(s * STAGE_BYTES + (k - kb) * ROW);
+        bulk_copy(sK + dst, k_pages + src, (uint32_t)n * ROW, bar);
+        bulk_copy(sV + dst, v_pages + src, (uint32_t)n * ROW, bar);
+        k += n;
+      }
+    } else {
+      // hg heads: whole pages (kb is a multiple of page_size), hg * page_size rows per copy
+      const int n_pg = (ke - kb + page_size - 1) / page_size;
+      const uint32_t chunk_bytes = (uint32_t)(hg * page_size) * ROW;
+      mbar_expect(bar, (uint32_t)n_pg * chunk_bytes * 2);
+      for (int j = 0; j < n_pg; ++j) {
+        const int page = s_pages[kb / page_size + j - first_page];
+        const size_t src = ((size_t)page * nkv + kvh0) * page_size * D;
+        const uint32_t dst = (uint32_t)(s * STAGE_BYTES) + (uint32_t)j * chunk_bytes;
+        bulk_copy(sK + dst, k_pages + src, chunk_bytes, bar);
+        bulk_copy(sV + dst, v_pages + src, chunk_bytes, bar);
+      }
     }
   };
   if (tid == 0) {
@@ -464,48 +504,78 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   }
 
   bool ok = true;
+  // this lane group's first key (of its head) inside a stage, and where that row sits in the stage:
+  // with hg > 1 a stage holds pages one after the other, each page holding its hg heads in turn
+  const int key_in_stage = ((warp % warps_per_head) * GPW + sub) * kKeysPerGroup;
+  const int row_offset = (hg == 1) ? key_in_stage * ROW
+                                   : ((key_in_stage / page_size) * hg * page_size + hh * page_size +
+                                      key_in_stage % page_size) * ROW;
+  const uint32_t group_mask = (LPK == 32 ? 0xffffffffu : ((1u << LPK) - 1u)) << (sub * LPK);   // lanes of this key group
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int s = tile % kStages;
     if (ok && !mbar_wait(sBar + 8 * s, (tile / kStages) & 1)) ok = false;
-    if (ok) {
-      const int kb = begin + tile * STAGE_KEYS;
-      const int n_here = min(end - kb, STAGE_KEYS);
-      const uint8_t* kt = smem + s * STAGE_BYTES;
-      const uint8_t* vt = smem + kStages * STAGE_BYTES + s * STAGE_BYTES;
-      // warp w takes keys w*KPW + sub, then strides by 4*KPW
-      for (int kk = warp * KPW + sub; kk < STAGE_KEYS; kk += 4 * KPW) {
-        const bool valid = kk < n_here;                     // uniform per LPK-lane group
-        float kf[8], vf[8];
-        if (valid) {
-          load8(reinterpret_cast<const __nv_bfloat16*>(kt + kk * ROW) + chunk * 8, kf);
-          load8(reinterpret_cast<const __nv_bfloat16*>(vt + kk * ROW) + chunk * 8, vf);
-        } else {
+    const int n_here = min(end - (begin + tile * STAGE_KEYS), STAGE_KEYS);
+    if (ok && key_in_stage < n_here) {
+      const uint8_t* kt = smem + s * STAGE_BYTES + row_offset + chunk * 16;
+      const uint8_t* vt = kt + kStages * STAGE_BYTES;
+      uint4 kraw[kKeysPerGroup];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+      for (int u = 0; u < kKeysPerGroup; ++u) kraw[u] = *reinterpret_cast<const uint4*>(kt + u * ROW);
+      float sc[R][kKeysPerGroup];
+#pragma unroll
+      for (int u = 0; u < kKeysPerGroup; ++u) {
+        float kf[8];
+        unpack8(kraw[u], kf);
+#pragma unroll
+        for (int g = 0; g < R; ++g) {
+          float d = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) d = fmaf(qr[g][i], kf[i], d);
+          sc[g][u] = d;
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < LPK; o <<= 1) {
+#pragma unroll
+        for (int g = 0; g < R; ++g) {
+#pragma unroll
+          for (int u = 0; u < kKeysPerGroup; ++u) sc[g][u] += __shfl_xor_sync(group_mask, sc[g][u], o);
+        }
+      }
+      uint4 vraw[kKeysPerGroup];
+#pragma unroll
+      for (int u = 0; u < kKeysPerGroup; ++u) vraw[u] = *reinterpret_cast<const uint4*>(vt + u * ROW);
+      float p[R][kKeysPerGroup];
+#pragma unroll
+      for (int g = 0; g < R; ++g) {
+        float m_new = m_run[g];
+#pragma unroll
+        for (int u = 0; u < kKeysPerGroup; ++u) {
+          if (key_in_stage + u >= n_here) sc[g][u] = -INFINITY;     // keys past the end of the split
+          m_new = fmaxf(m_new, sc[g][u]);
+        }
+        // key_in_stage < n_here: at least one key is real, so m_new is finite
+        const float a = exp2f(m_run[g] - m_new);
+        float sum = 0.f;
+#pragma unroll
+        for (int u = 0; u < kKeysPerGroup; ++u) { p[g][u] = exp2f(sc[g][u] - m_new); sum += p[g][u]; }
+        l_run[g] = l_run[g] * a + sum;
+        m_run[g] = m_new;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] *= a;
+      }
+#pragma unroll
+      for (int u = 0; u < kKeysPerGroup; ++u) {
+        float vf[8];
+        unpack8(vraw[u], vf);
+        if (key_in_stage + u >= n_here) {                           // unwritten rows may hold anything
+#pragma unroll
+          for (int i = 0; i < 8; ++i) vf[i] = 0.f;
         }
 #pragma unroll
         for (int g = 0; g < R; ++g) {
-          float sc = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) sc = fmaf(qr[g][i], kf[i], sc);
-#pragma unroll
-          for (int o = 1; o < LPK; o <<= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
-          if (valid) {
-            float p;
-            if (sc > m_run[g]) {
-              const float a = exp2f(m_run[g] - sc);
-              l_run[g] *= a;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) acc[g][i] *= a;
-              m_run[g] = sc;
-              p = 1.f;
-            } else {
-              p = exp2f(sc - m_run[g]);
-            }
-            l_run[g] += p;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i]);
-          }
+          for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p[g][u], vf[i], acc[g][i]);
         }
       }
     }
@@ -513,7 +583,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
     if (tid == 0 && ok && tile + kStages < n_tiles) issue(tile + kStages);
   }
 
-  // Merge the KPW key groups of each warp (lanes that share `chunk`), then the four warps.
+  // Merge the lane groups of each warp (lanes that share `chunk`), then the warps.
 #pragma unroll
   for (int g = 0; g < R; ++g) {
     float m = m_run[g];
@@ -542,43 +612,57 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
     if (tid == 0) atomicCAS(status, 0, 2000000 + (int)blockIdx.x);
     return;
   }
-  for (int idx = tid; idx < R * D; idx += kDecThreads) {
-    const int g = idx / D, d = idx % D;
+  for (int idx = tid; idx < hg * R * D; idx += kDecThreads) {
+    const int head = idx / (R * D), g = (idx / D) % R, d = idx % D;
+    const int w0 = head * warps_per_head;
     float m = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge[(w * R + g) * (D + 2) + D]);
+    for (int w = w0; w < w0 + warps_per_head; ++w) m = fmaxf(m, merge[(w * R + g) * (D + 2) + D]);
     float sum = 0.f, l = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = w0; w < w0 + warps_per_head; ++w) {
       const float mw = merge[(w * R + g) * (D + 2) + D];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
       sum += merge[(w * R + g) * (D + 2) + d] * f;
       l += merge[(w * R + g) * (D + 2) + D + 1] * f;
     }
-    const size_t slot = ((size_t)seq * nq + kvh * R + g) * max_splits + split;
+    const size_t slot = ((size_t)seq * nq + (kvh0 + head) * R + g) * max_splits + split;
     part_acc[slot * D + d] = sum;
     if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
   }
 }
 
-// Merges the splits of each (sequence, head) in order.  The partial maxima are in the log2 domain.
-__global__ void attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                                     const int* __restrict__ token_of_seq, const int* __restrict__ positions,
-                                                     __nv_bfloat16* __restrict__ out, int out_row_stride, int max_splits,
-                                                     int nq, int head_dim, int split_keys) {
-  const int h = blockIdx.x, seq = blockIdx.y;
+// Merges the splits of each (sequence, head).  The partial maxima are in the log2 domain.  The
+// weights of the splits are computed by the first lanes in parallel; every output element is then
+// a sum over the splits in their order.
+constexpr int kCombineMaxSplits = 64;
+__global__ void __launch_bounds__(64)
+attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                     const int* __restrict__ token_of_seq, const int* __restrict__ positions,
+                                     __nv_bfloat16* __restrict__ out, int out_row_stride, int max_splits,
+                                     int nq, int head_dim, int split_keys) {
+  __shared__ float s_w[kCombineMaxSplits];
+  __shared__ float s_red[2];
+  const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
   const int t = token_of_seq[seq];
   const int n_splits = positions[t] / split_keys + 1;
   const size_t base = ((size_t)seq * nq + h) * max_splits;
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
-  float l = 0.f;
-  for (int s = 0; s < n_splits; ++s) l += part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - m);
-  const float inv = 1.f / l;
+  float m_i = -INFINITY, l_i = 0.f;
+  if (tid < n_splits) { m_i = part_ml[(base + tid) * 2]; l_i = part_ml[(base + tid) * 2 + 1]; }
+  float m = warp_max(m_i);
+  if ((tid & 31) == 0) s_red[tid >> 5] = m;
+  __syncthreads();
+  m = fmaxf(s_red[0], s_red[1]);
+  const float w_i = (tid < n_splits) ? exp2f(m_i - m) : 0.f;
+  if (tid < kCombineMaxSplits) s_w[tid] = w_i;
+  float l = warp_sum(l_i * w_i);
+  __syncthreads();
+  if ((tid & 31) == 0) s_red[tid >> 5] = l;
+  __syncthreads();
+  const float inv = 1.f / (s_red[0] + s_red[1]);
   __nv_bfloat16* o = out + (size_t)t * out_row_stride + (size_t)h * head_dim;
-  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+  for (int d = tid; d < head_dim; d += 64) {
     float sum = 0.f;
-    for (int s = 0; s < n_splits; ++s) sum += part_acc[(base + s) * head_dim + d] * exp2f(part_ml[(base + s) * 2] - m);
+#pragma unroll 8
+    for (int s = 0; s < n_splits; ++s) sum += part_acc[(base + s) * head_dim + d] * s_w[s];
     o[d] = __float2bfloat16_rn(sum * inv);
   }
 }
@@ -588,18 +672,27 @@ int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, con
                        const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                        float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
                        int split_keys, float scale_log2, int* status, cudaStream_t s) {
-  constexpr int STAGE_BYTES = (4096 / D) * D * 2;
-  const size_t smem = 2 * kStages * STAGE_BYTES + 64 + (size_t)4 * R * (D + 2) * sizeof(float) + 128;
+  // Heads per block: enough neighbouring kv heads that one page's rows make a copy of about 8 KB,
+  // as long as whole pages tile a stage and the split.
+  constexpr int STAGE_ROWS = kDecWarps * (32 / (D / 8)) * kKeysPerGroup;
+  int hg = 1;
+  while (hg < kDecWarps && hg * 2 * page_size * D * 2 <= 8192 && nkv % (hg * 2) == 0 &&
+         (STAGE_ROWS / (hg * 2)) % page_size == 0 && split_keys % page_size == 0)
+    hg *= 2;
+  constexpr int STAGE_BYTES = kDecWarps * (32 / (D / 8)) * kKeysPerGroup * D * 2;
+  const size_t smem = 2 * kStages * STAGE_BYTES + 64 + (size_t)kDecWarps * R * (D + 2) * sizeof(float) + 128 +
+                      (size_t)(split_keys / page_size + 2) * sizeof(int);
+  if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: split of %d keys in pages of %d", split_keys, page_size);
   auto kern = attention_decode_bulk_kernel<D, R>;
-  static bool configured = false;
-  if (!configured) {
+  static size_t configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_decode_bulk: %s", cudaGetErrorString(e));
-    configured = true;
+    configured = smem;
   }
-  kern<<<dim3(max_splits, nkv, n_seqs), kDecThreads, smem, s>>>((const __nv_bfloat16*)q, q_row_stride,
+  kern<<<dim3(max_splits, nkv / hg, n_seqs), kDecThreads, smem, s>>>((const __nv_bfloat16*)q, q_row_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, token_of_seq, positions,
-      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, status);
+      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, status);
   return check_launch("attention_decode_bulk");
 }
 
@@ -634,6 +727,8 @@ ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const 
   if (q_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
     return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: rows must be 16-byte aligned");
   if (n_seqs > 65535 || nkv > 65535) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: grid too large");
+  if (max_splits > kCombineMaxSplits)
+    return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: %d splits (at most %d)", max_splits, kCombineMaxSplits);
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
   const int r = nq / nkv;

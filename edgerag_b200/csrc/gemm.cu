@@ -116,3 +116,124 @@ ERB_EXPORT int erb_linear(const void* a, const void* w, void* out, int M, int N,
                           workspace, ws, (cudaStream_t)stream));
   return ERB_OK;
 }
+
+#if ERB_ELEM == 1
+// ---------------------------------------------------------------------------------------------
+// Weight-streaming product for a handful of rows (decode): out[M, N] = a[M, K] * w[N, K]^T with
+// M <= 16, bfloat16 operands, float accumulation.  The work is reading w once at memory speed:
+// each warp owns two rows of w and walks K with 16-byte loads, eight chunks per row in flight
+// before any is used; the few rows of `a` are re-read from L1.  Sums are reduced over the warp
+// in a fixed order, so the result does not depend on the launch geometry.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kSkWarps = 8;
+constexpr int kSkRows = 2;       // rows of w per warp
+constexpr int kSkUnroll = 4;     // 16-byte chunks per row and lane in flight
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* f) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <int MT, bool OUT_F32>
+__global__ void __launch_bounds__(kSkWarps * 32)
+linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
+                     int M, int N, int K, int lda, int ldw, int ldo) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * kSkWarps + warp) * kSkRows;
+  if (n0 >= N) return;
+  float acc[MT][kSkRows];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int r = 0; r < kSkRows; ++r) acc[m][r] = 0.f;
+  const __nv_bfloat16* wr[kSkRows];
+#pragma unroll
+  for (int r = 0; r < kSkRows; ++r) wr[r] = w + (size_t)min(n0 + r, N - 1) * ldw;
+
+  const int chunks = K >> 3;                     // 16-byte chunks per row
+  for (int c0 = lane; c0 < chunks; c0 += 32 * kSkUnroll) {
+    uint4 raw[kSkRows][kSkUnroll];
+#pragma unroll
+    for (int u = 0; u < kSkUnroll; ++u) {
+      const int c = c0 + 32 * u;
+#pragma unroll
+      for (int r = 0; r < kSkRows; ++r)
+        raw[r][u] = (c < chunks) ? __ldcs(reinterpret_cast<const uint4*>(wr[r]) + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kSkUnroll; ++u) {
+      const int c = c0 + 32 * u;
+      if (c >= chunks) break;
+      float wf[kSkRows][8];
+#pragma unroll
+      for (int r = 0; r < kSkRows; ++r) unpack_bf16x8(raw[r][u], wf[r]);
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m < M) {
+          float xf[8];
+          unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(a + (size_t)m * lda) + c), xf);
+#pragma unroll
+          for (int r = 0; r < kSkRows; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[m][r] = fmaf(xf[i], wf[r][i], acc[m][r]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int r = 0; r < kSkRows; ++r) acc[m][r] = warp_sum(acc[m][r]);
+  if (lane == 0) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      if (m >= M) break;
+#pragma unroll
+      for (int r = 0; r < kSkRows; ++r) {
+        if (n0 + r < N) {
+          if (OUT_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n0 + r] = acc[m][r];
+          else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n0 + r] = __float2bfloat16_rn(acc[m][r]);
+        }
+      }
+    }
+  }
+}
+
+template <int MT>
+int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw, int ldo,
+                  int out_f32, cudaStream_t s) {
+  const int rows_per_block = kSkWarps * kSkRows;
+  const unsigned blocks = (unsigned)((N + rows_per_block - 1) / rows_per_block);
+  if (out_f32)
+    linear_skinny_kernel<MT, true><<<blocks, kSkWarps * 32, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+                                                                     out, M, N, K, lda, ldw, ldo);
+  else
+    linear_skinny_kernel<MT, false><<<blocks, kSkWarps * 32, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+                                                                      out, M, N, K, lda, ldw, ldo);
+  return check_launch("linear_skinny");
+}
+
+}  // namespace
+
+// Same result contract as erb_linear (no accumulate), for 1 <= M <= 16 with K, lda and ldw
+// multiples of 8 elements and 16-byte aligned operands.
+ERB_EXPORT int erb_linear_skinny(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw,
+                                 int ldo, int out_f32, void* stream) {
+  if (M <= 0) return ERB_OK;
+  if (M > 16) return fail(ERB_ERR_UNSUPPORTED, "linear_skinny: %d rows (at most 16)", M);
+  if (N <= 0 || K <= 0 || lda < K || ldw < K || ldo < N) return fail(ERB_ERR_ARG, "linear_skinny: bad sizes");
+  if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15))
+    return fail(ERB_ERR_UNSUPPORTED, "linear_skinny: K and the leading dimensions must be multiples of 8");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (M <= 2) return launch_skinny<2>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+  if (M <= 4) return launch_skinny<4>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+  if (M <= 8) return launch_skinny<8>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+  return launch_skinny<16>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+}
+#endif  // ERB_ELEM == 1

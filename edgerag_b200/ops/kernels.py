@@ -41,6 +41,9 @@ _SIGNATURES = {
     "erb_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                  c_void_p],
+    "erb_attention_decode_bulk": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_int, c_float, c_void_p, c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
@@ -48,7 +51,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_attention_decode": 2, "erb_linear": 0}
+_LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 2, "erb_linear": 0}
 
 
 def _fn(library: str, elem: str | None, name: str):
@@ -226,6 +229,8 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate:
 
 # --- attention -------------------------------------------------------------------------------
 
+DECODE_SPLIT_KEYS = 512
+
 def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                    seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
                    scale: float, window: int = 0) -> None:
@@ -246,9 +251,6 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_of_token.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), n, n_q_heads, nkv, d, page_size, int(window),
           float(scale), _stream())
-
-
-DECODE_SPLIT_KEYS = 512
 
 
 def decode_scratch_floats(n_seqs: int, n_q_heads: int, head_dim: int, max_splits: int) -> tuple[int, int]:
@@ -280,6 +282,36 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(),
           max_splits, n_seqs, n_q_heads, nkv, d, page_size, int(window), int(split_keys), float(scale), _stream())
+
+
+def decode_bulk_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_heads: int, n_kv_heads: int,
+                          max_splits: int = 1) -> bool:
+    """Shapes the bulk-copy decode kernel takes; everything else goes to the general decode kernel."""
+    return (dtype == torch.bfloat16 and head_dim in (32, 64, 128) and window <= 0
+            and n_q_heads // n_kv_heads <= 8 and max_splits <= 64)
+
+
+def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                          token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
+                          scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
+                          status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS) -> None:
+    """``attention_decode`` for bfloat16 with keys and values streamed by bulk asynchronous copies."""
+    _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pages, "k_pages", torch.bfloat16)
+    _need(v_pages, "v_pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
+    _need(token_of_seq, "token_of_seq", torch.int32); _need(positions, "positions", torch.int32)
+    _need(out, "out", torch.bfloat16, contiguous=False); _need(part_acc, "part_acc", torch.float32)
+    _need(part_ml, "part_ml", torch.float32); _need(status, "status", torch.int32)
+    n_seqs = token_of_seq.numel()
+    _, nkv, page_size, d = k_pages.shape
+    need_acc, need_ml = decode_scratch_floats(n_seqs, n_q_heads, d, max_splits)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
+        raise KernelError("attention_decode_bulk: scratch too small")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention_decode_bulk: q/out inner stride must be 1")
+    _call(_fn("attention_tc", None, "erb_attention_decode_bulk"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
+          v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
+          positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
+          n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(), _stream())
 
 
 def prefill_tc_supported(dtype: torch.dtype, head_dim: int, window: int) -> bool:

@@ -1,0 +1,160 @@
+"""Time one kernel of the engine in isolation, on the device clock, against its roofline.
+
+    python -m edgerag_b200.ops.microbench decode-attention --batch 8 --context 8192
+    python -m edgerag_b200.ops.microbench prefill-attention --tokens 2048
+    python -m edgerag_b200.ops.microbench linear --m 8 --n 6144 --k 2048
+
+Each case builds random inputs larger than the 126 MB L2 where the real workload is (or says that
+it is not), runs warm-up launches, then times ``--iters`` launches one by one with CUDA events and
+prints one JSON line with the median.  The same commands, under ``ncu``, produce the summaries in
+``profiles/``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+
+import torch
+
+from . import kernels
+
+HBM_GBS, BF16_TFLOPS = 6650.0, 1590.0   # the pool's earlier measurement, used when no measured file is given
+
+
+def _time(fn, iters: int, warmup: int, rounds: int = 5) -> float:
+    """Median over ``rounds`` of the time per launch of ``iters`` launches issued back to back, in
+    microseconds (one launch at a time would time the host's launch path, not the kernel)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(rounds):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3 / iters)
+    return statistics.median(times)
+
+
+def _paged(batch: int, context: int, nkv: int, d: int, page: int, dtype, shuffle: bool = True):
+    pages_per = -(-context // page)
+    n_pages = batch * pages_per
+    kp = torch.randn((n_pages, nkv, page, d), device="cuda", dtype=torch.float32).to(dtype)
+    vp = torch.randn((n_pages, nkv, page, d), device="cuda", dtype=torch.float32).to(dtype)
+    order = torch.randperm(n_pages) if shuffle else torch.arange(n_pages)
+    tables = order.view(batch, pages_per).to(torch.int32).cuda()
+    return kp, vp, tables
+
+
+def decode_attention(a) -> dict:
+    dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    kp, vp, tables = _paged(a.batch, a.context, a.kv_heads, a.head_dim, a.page, dtype, not a.sequential_pages)
+    q = torch.randn((a.batch, a.heads * a.head_dim), device="cuda").to(dtype)
+    out = torch.empty_like(q)
+    pos = torch.full((a.batch,), a.context - 1, dtype=torch.int32, device="cuda")
+    tok = torch.arange(a.batch, dtype=torch.int32, device="cuda")
+    splits = (a.context - 1) // a.split + 1
+    acc_n, ml_n = kernels.decode_scratch_floats(a.batch, a.heads, a.head_dim, splits)
+    acc, ml = torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scale = a.head_dim ** -0.5
+    if a.kernel == "bulk":
+        fn = lambda: kernels.attention_decode_bulk(q, kp, vp, tables, tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
+                                                   status, split_keys=a.split)
+    else:
+        fn = lambda: kernels.attention_decode(q, kp, vp, tables, tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
+                                              split_keys=a.split)
+    us = _time(fn, a.iters, a.warmup)
+    nbytes = 2 * a.batch * a.context * a.kv_heads * a.head_dim * kp.element_size()
+    return {"case": "decode-attention", "kernel": a.kernel, "us": round(us, 2), "bytes": nbytes,
+            "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
+            "status": int(status), "larger_than_l2": nbytes > 126e6}
+
+
+def prefill_attention(a) -> dict:
+    dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    total = a.past + a.tokens
+    kp, vp, tables = _paged(1, total, a.kv_heads, a.head_dim, a.page, dtype, not a.sequential_pages)
+    width = (a.heads + 2 * a.kv_heads) * a.head_dim
+    qkv = torch.randn((a.tokens, width), device="cuda").to(dtype)
+    out = torch.empty((a.tokens, a.heads * a.head_dim), device="cuda", dtype=dtype)
+    pos = torch.arange(a.past, total, dtype=torch.int32, device="cuda")
+    starts = torch.tensor([0, a.tokens], dtype=torch.int32, device="cuda")
+    seq_of = torch.zeros(a.tokens, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scale = a.head_dim ** -0.5
+    if a.kernel == "tc":
+        fn = lambda: kernels.attention_prefill_tc(qkv, kp, vp, tables, starts, pos, out, -(-a.tokens // 128), a.heads,  # noqa: E731
+                                                  scale, status)
+    else:
+        fn = lambda: kernels.attention_rows(qkv, kp, vp, tables, seq_of, pos, out, a.heads, scale)  # noqa: E731
+    us = _time(fn, a.iters, a.warmup)
+    pairs = a.tokens * a.past + a.tokens * (a.tokens + 1) / 2
+    flops = 4.0 * a.heads * a.head_dim * pairs
+    return {"case": "prefill-attention", "kernel": a.kernel, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+            "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4), "status": int(status)}
+
+
+def linear(a) -> dict:
+    dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    reps = max(1, int(200e6 // (a.n * a.k * 2)) + 1)    # rotate over several weight copies: more than L2 in total
+    ws = [torch.randn((a.n, a.k), device="cuda").to(dtype) for _ in range(reps)]
+    x = torch.randn((a.m, a.k), device="cuda").to(dtype)
+    out = torch.empty((a.m, a.n), device="cuda", dtype=torch.float32 if a.out32 else dtype)
+    state = {"i": 0}
+
+    def fn():
+        state["i"] = (state["i"] + 1) % reps
+        kernels.linear(x, ws[state["i"]], out)
+
+    us = _time(fn, a.iters, a.warmup)
+    nbytes = a.n * a.k * x.element_size() + a.m * a.k * x.element_size() + out.numel() * out.element_size()
+    flops = 2.0 * a.m * a.n * a.k
+    return {"case": "linear", "m": a.m, "n": a.n, "k": a.k, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+            "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4), "tflops": round(flops / us / 1e6, 2)}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="edgerag_b200.ops.microbench", description=__doc__.split("\n\n")[0])
+    sub = ap.add_subparsers(dest="case", required=True)
+    common = argparse.ArgumentParser(add_help=False)
+    common.add_argument("--iters", type=int, default=20)
+    common.add_argument("--warmup", type=int, default=3)
+    common.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    att = argparse.ArgumentParser(add_help=False)
+    att.add_argument("--heads", type=int, default=32)
+    att.add_argument("--kv-heads", type=int, default=32)
+    att.add_argument("--head-dim", type=int, default=64)
+    att.add_argument("--page", type=int, default=16)
+    att.add_argument("--sequential-pages", action="store_true", help="pages in order instead of shuffled")
+    d = sub.add_parser("decode-attention", parents=[common, att])
+    d.add_argument("--batch", type=int, default=8)
+    d.add_argument("--context", type=int, default=8192)
+    d.add_argument("--split", type=int, default=kernels.DECODE_SPLIT_KEYS)
+    d.add_argument("--kernel", choices=["bulk", "general"], default="bulk")
+    p = sub.add_parser("prefill-attention", parents=[common, att])
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--past", type=int, default=0)
+    p.add_argument("--kernel", choices=["tc", "general"], default="tc")
+    g = sub.add_parser("linear", parents=[common])
+    g.add_argument("--m", type=int, default=8)
+    g.add_argument("--n", type=int, default=6144)
+    g.add_argument("--k", type=int, default=2048)
+    g.add_argument("--out32", action="store_true")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("microbench needs a CUDA device", file=sys.stderr)
+        return 1
+    fn = {"decode-attention": decode_attention, "prefill-attention": prefill_attention, "linear": linear}[a.case]
+    print(json.dumps(fn(a)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

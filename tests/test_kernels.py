@@ -246,6 +246,33 @@ def test_attention_decode(k, dtype, nq, nkv, d, ps, window, split):
     torch.testing.assert_close(out2.float(), out.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize("nq,nkv,d,ps,split", [(4, 4, 64, 16, 512), (6, 2, 64, 4, 128), (8, 1, 128, 16, 512),
+                                               (2, 2, 32, 64, 256), (5, 5, 64, 24, 512), (8, 8, 64, 16, 512),
+                                               (16, 8, 64, 8, 512), (4, 4, 128, 16, 256)])
+def test_attention_decode_bulk_copies(k, nq, nkv, d, ps, split):
+    """The decode kernel that streams pages with bulk asynchronous copies: lengths around stage and
+    split edges, grouped heads, page sizes that do and do not divide a stage, NaN in unwritten slots."""
+    dtype = torch.bfloat16
+    ctx_lens = [1, 63, 64, 65, 1300, 512, 513, 129]
+    case = paged_case(dtype, 90 + d + ps, nq, nkv, d, ps, ctx_lens, [1] * len(ctx_lens))
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    n = len(ctx_lens)
+    max_splits = max((c - 1) // split + 1 for c in ctx_lens)
+    acc_n, ml_n = k.decode_scratch_floats(n, nq, d, max_splits)
+    part_acc = torch.full((acc_n,), float("nan"), device="cuda")
+    part_ml = torch.full((ml_n,), float("nan"), device="cuda")
+    out = torch.full((n, nq * d), float("nan"), dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tok = torch.arange(n, dtype=torch.int32).cuda()
+    k.attention_decode_bulk(dev["q"], dev["kp"], dev["vp"], dev["tables"], tok, dev["pos"], out, nq, scale,
+                            part_acc, part_ml, max_splits, status, split_keys=split)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    want = attention_reference(case, nq, nkv, d, scale)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key(k, dtype):
     """One key far back, in the first page, gets a score that stands out: the output must be its value.
