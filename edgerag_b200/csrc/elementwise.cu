@@ -79,6 +79,64 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
   }
 }
 
+// Four elements per thread and step (hidden_size a multiple of 4): 16-byte accesses to the residual.
+template <typename T> struct Pack4;
+template <> struct Pack4<float> {
+  static __device__ __forceinline__ void load(const float* p, float* v) { load4(p, v); }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Pack4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xffff0000u);
+    v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+  }
+};
+
+template <typename T>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
+                                        const float* __restrict__ weight, T* __restrict__ out,
+                                        const int* __restrict__ rows, int hidden_size, float eps,
+                                        int write_back) {
+  extern __shared__ float row_cache[];
+  float* scratch = row_cache + hidden_size;
+  const int o = blockIdx.x;
+  const int r = rows ? rows[o] : o;
+  float* h = hidden + (size_t)r * hidden_size;
+  const T* d = delta ? delta + (size_t)r * hidden_size : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < hidden_size; i += blockDim.x * 4) {
+    float v[4];
+    load4(h + i, v);
+    if (d) {
+      float dv[4];
+      Pack4<T>::load(d + i, dv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] += dv[j];
+      if (write_back) *reinterpret_cast<float4*>(h + i) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    *reinterpret_cast<float4*>(row_cache + i) = make_float4(v[0], v[1], v[2], v[3]);
+    ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+  }
+  const float total = block_sum(ss, scratch);
+  const float rs = rsqrtf(total / (float)hidden_size + eps);
+  T* y = out + (size_t)o * hidden_size;
+  for (int i = threadIdx.x * 4; i < hidden_size; i += blockDim.x * 4) {
+    float v[4], w[4];
+    load4(row_cache + i, v);
+    load4(weight + i, w);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = w[j] * Elem<T>::round(v[j] * rs);
+    Pack4<T>::store(y + i, v);
+  }
+}
+
 ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* weight, void* out,
                                const int* rows, int n_rows, int hidden_size, float eps, int write_back,
                                void* stream) {
@@ -92,8 +150,20 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "add_rmsnorm: %s", cudaGetErrorString(e));
   }
-  add_rmsnorm_kernel<elem_t><<<n_rows, threads, smem, (cudaStream_t)stream>>>((float*)hidden,
-      (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+  const bool vec = hidden_size % 4 == 0 && !((uintptr_t)hidden & 15) && !((uintptr_t)delta & 7) &&
+                   !((uintptr_t)out & 7) && !((uintptr_t)weight & 15);
+  if (vec) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "add_rmsnorm: %s", cudaGetErrorString(e));
+    }
+    add_rmsnorm_vec4_kernel<elem_t><<<n_rows, threads, smem, (cudaStream_t)stream>>>((float*)hidden,
+        (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+  } else {
+    add_rmsnorm_kernel<elem_t><<<n_rows, threads, smem, (cudaStream_t)stream>>>((float*)hidden,
+        (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+  }
   return check_launch("add_rmsnorm");
 }
 
@@ -174,6 +244,57 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
   }
 }
 
+// Full rotation (rot_dim == head_dim, a multiple of 8): the angles of a token are computed once per
+// block into shared memory, every work item moves four consecutive elements of each half, and the
+// heads of a token are spread over gridDim.y blocks so that a few decode tokens still fill the GPU.
+template <typename T>
+__global__ void rope_cache_write_vec4_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                             const float* __restrict__ inv_freq, const int* __restrict__ slots,
+                                             T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
+                                             int head_dim, int page_size, int write_kv) {
+  extern __shared__ float trig[];            // cos[half], sin[half]
+  const int t = blockIdx.x;
+  const int half = head_dim / 2;
+  const float pos = (float)positions[t];
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], trig + half + j, trig + j);
+  __syncthreads();
+  const int row_width = (nq + 2 * nkv) * head_dim;
+  T* row = qkv + (size_t)t * row_width;
+  const int slot = (write_kv && slots) ? slots[t] : -1;
+  const int page = slot >= 0 ? slot / page_size : 0;
+  const int offset = slot >= 0 ? slot % page_size : 0;
+  const int per_head = half / 4;              // items per rotated head
+  const int rot_items = (nq + nkv) * per_head;
+  const int v_items = slot >= 0 ? nkv * head_dim / 4 : 0;
+  const int stride = gridDim.y * blockDim.x;
+  for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < rot_items + v_items; w += stride) {
+    if (w < rot_items) {
+      const int head = w / per_head, j = (w % per_head) * 4;
+      if (head >= nq && slot < 0) continue;
+      T* x = row + (size_t)head * head_dim;
+      float a[4], b[4], lo[4], hi[4];
+      Pack4<T>::load(x + j, a);
+      Pack4<T>::load(x + j + half, b);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float cs = trig[j + i], sn = trig[half + j + i];
+        lo[i] = a[i] * cs - b[i] * sn;
+        hi[i] = b[i] * cs + a[i] * sn;
+      }
+      T* dst = x;
+      if (head >= nq) dst = k_pages + (((size_t)page * nkv + (head - nq)) * page_size + offset) * head_dim;
+      Pack4<T>::store(dst + j, lo);
+      Pack4<T>::store(dst + j + half, hi);
+    } else {
+      const int i = (w - rot_items) * 4;
+      const int kvh = i / head_dim, e = i % head_dim;
+      float v[4];
+      Pack4<T>::load(row + (size_t)(nq + nkv) * head_dim + i, v);
+      Pack4<T>::store(v_pages + (((size_t)page * nkv + kvh) * page_size + offset) * head_dim + e, v);
+    }
+  }
+}
+
 ERB_EXPORT int erb_rope_cache_write(void* qkv, const int* positions, const float* inv_freq,
                                     const int* slots, void* k_pages, void* v_pages, int n_tokens,
                                     int nq, int nkv, int head_dim, int rot_dim, int page_size,
@@ -186,6 +307,18 @@ ERB_EXPORT int erb_rope_cache_write(void* qkv, const int* positions, const float
     return fail(ERB_ERR_ARG, "rope_cache_write: cache arguments missing");
   const int work = (nq + nkv) * head_dim / 2;
   const int threads = work >= 512 ? 256 : 128;
+  if (rot_dim == head_dim && head_dim % 8 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)k_pages & 15) &&
+      !((uintptr_t)v_pages & 15)) {
+    const int items = (nq + nkv) * head_dim / 8 + nkv * head_dim / 4;
+    int y = (items + 127) / 128;
+    const int want = (148 * 8 + n_tokens - 1) / n_tokens;      // enough blocks for every SM
+    if (y > want) y = want;
+    if (y < 1) y = 1;
+    rope_cache_write_vec4_kernel<elem_t><<<dim3(n_tokens, y), 128, head_dim * sizeof(float), (cudaStream_t)stream>>>(
+        (elem_t*)qkv, positions, inv_freq, slots, (elem_t*)k_pages, (elem_t*)v_pages, nq, nkv, head_dim, page_size,
+        write_kv);
+    return check_launch("rope_cache_write");
+  }
   rope_cache_write_kernel<elem_t><<<n_tokens, threads, 0, (cudaStream_t)stream>>>((elem_t*)qkv, positions,
       inv_freq, slots, (elem_t*)k_pages, (elem_t*)v_pages, nq, nkv, head_dim, rot_dim, page_size, write_kv);
   return check_launch("rope_cache_write");
@@ -206,11 +339,49 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   Elem<T>::store(out + idx, act * u);
 }
 
+template <typename T> struct Vec16;   // 16-byte groups
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* v) { load4(p, v); }
+  static __device__ __forceinline__ void store(float* p, const float* v) { Pack4<float>::store(p, v); }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) { load8(p, v); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    Pack4<__nv_bfloat16>::store(p, v);
+    Pack4<__nv_bfloat16>::store(p + 4, v + 4);
+  }
+};
+
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t groups) {
+  constexpr int N = Vec16<T>::N;
+  const size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gidx >= groups) return;
+  const int per_row = inter / N;
+  const size_t t = gidx / per_row;
+  const int i = (int)(gidx % per_row) * N;
+  const T* row = gate_up + t * 2 * (size_t)inter;
+  float g[N], u[N];
+  Vec16<T>::load(row + i, g);
+  Vec16<T>::load(row + inter + i, u);
+#pragma unroll
+  for (int j = 0; j < N; ++j) g[j] = g[j] / (1.f + expf(-g[j])) * u[j];
+  Vec16<T>::store(out + t * (size_t)inter + i, g);
+}
+
 ERB_EXPORT int erb_swiglu(const void* gate_up, void* out, int n_tokens, int inter, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   if (inter <= 0) return fail(ERB_ERR_ARG, "swiglu: bad intermediate size");
   const size_t total = (size_t)n_tokens * inter;
   const int threads = 256;
+  if (inter % Vec16<elem_t>::N == 0 && !((uintptr_t)gate_up & 15) && !((uintptr_t)out & 15)) {
+    const size_t groups = total / Vec16<elem_t>::N;
+    swiglu_vec_kernel<elem_t><<<(unsigned)((groups + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
+        (const elem_t*)gate_up, (elem_t*)out, inter, groups);
+    return check_launch("swiglu");
+  }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   swiglu_kernel<elem_t><<<blocks, threads, 0, (cudaStream_t)stream>>>((const elem_t*)gate_up, (elem_t*)out,
                                                                      inter, total);

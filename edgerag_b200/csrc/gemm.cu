@@ -119,121 +119,129 @@ ERB_EXPORT int erb_linear(const void* a, const void* w, void* out, int M, int N,
 
 #if ERB_ELEM == 1
 // ---------------------------------------------------------------------------------------------
-// Weight-streaming product for a handful of rows (decode): out[M, N] = a[M, K] * w[N, K]^T with
-// M <= 16, bfloat16 operands, float accumulation.  The work is reading w once at memory speed:
-// each warp owns two rows of w and walks K with 16-byte loads, eight chunks per row in flight
-// before any is used; the few rows of `a` are re-read from L1.  Sums are reduced over the warp
-// in a fixed order, so the result does not depend on the launch geometry.
+// Weight-streaming product for few rows (decode): out[M, N] = a[M, K] * w[N, K]^T, M <= 64,
+// bfloat16 operands, float accumulation.  The work is reading w once at memory speed, so w is the
+// "A" operand of mma.sync.m16n8k16 (16 rows of w per block) and the few rows of `a` are the 8-wide
+// "B" operand: no shared-memory staging, every operand fragment is a plain 16-byte global load.
+//
+// Fragment trick: a dot product does not care in which order k is visited, as long as both
+// operands agree.  Lane (r = lane / 4, j = lane % 4) loads 8 consecutive k of w row r and of row
+// r + 8, and the same 8 k of `a` row r; elements 0..3 feed one mma (as the k = 2j, 2j+1, 2j+8,
+// 2j+9 slots of the instruction), elements 4..7 the next.  One pass covers 32 k with two mma.
+//
+// The eight warps of a block take passes round-robin (so together they read 512 contiguous bytes
+// of each row per round) and their partial sums are added in warp order through shared memory.
 // ---------------------------------------------------------------------------------------------
 namespace {
 
 constexpr int kSkWarps = 8;
-constexpr int kSkRows = 2;       // rows of w per warp
-constexpr int kSkUnroll = 4;     // 16-byte chunks per row and lane in flight
+constexpr int kSkUnroll = 4;     // passes in flight per warp
 
-__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* f) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
+__device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int MT, bool OUT_F32>
+template <int NT, bool OUT_F32>   // NT: tiles of 8 rows of `a`
 __global__ void __launch_bounds__(kSkWarps * 32)
 linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                      int M, int N, int K, int lda, int ldw, int ldo) {
+  __shared__ float red[kSkWarps][NT][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * kSkWarps + warp) * kSkRows;
-  if (n0 >= N) return;
-  float acc[MT][kSkRows];
+  const int r = lane >> 2, j = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const uint4* w_lo = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + r, N - 1) * ldw);
+  const uint4* w_hi = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + r + 8, N - 1) * ldw);
+  const uint4* a_row[NT];
+  bool a_ok[NT];
 #pragma unroll
-  for (int m = 0; m < MT; ++m)
+  for (int t = 0; t < NT; ++t) {
+    a_ok[t] = t * 8 + r < M;
+    a_row[t] = reinterpret_cast<const uint4*>(a + (size_t)(a_ok[t] ? t * 8 + r : 0) * lda);
+  }
+  float acc[NT][4];
 #pragma unroll
-    for (int r = 0; r < kSkRows; ++r) acc[m][r] = 0.f;
-  const __nv_bfloat16* wr[kSkRows];
+  for (int t = 0; t < NT; ++t)
 #pragma unroll
-  for (int r = 0; r < kSkRows; ++r) wr[r] = w + (size_t)min(n0 + r, N - 1) * ldw;
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
 
-  const int chunks = K >> 3;                     // 16-byte chunks per row
-  for (int c0 = lane; c0 < chunks; c0 += 32 * kSkUnroll) {
-    uint4 raw[kSkRows][kSkUnroll];
+  const int chunks = K >> 3;                          // 16-byte chunks per row
+  const int passes = (chunks + 3) >> 2;               // 4 chunks (32 k) per pass
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int p0 = warp; p0 < passes; p0 += kSkWarps * kSkUnroll) {
+    uint4 lo[kSkUnroll], hi[kSkUnroll];
 #pragma unroll
     for (int u = 0; u < kSkUnroll; ++u) {
-      const int c = c0 + 32 * u;
-#pragma unroll
-      for (int r = 0; r < kSkRows; ++r)
-        raw[r][u] = (c < chunks) ? __ldcs(reinterpret_cast<const uint4*>(wr[r]) + c) : make_uint4(0, 0, 0, 0);
+      const int c = (p0 + u * kSkWarps) * 4 + j;
+      const bool in = c < chunks;
+      lo[u] = in ? __ldcs(w_lo + c) : zero;
+      hi[u] = in ? __ldcs(w_hi + c) : zero;
     }
 #pragma unroll
     for (int u = 0; u < kSkUnroll; ++u) {
-      const int c = c0 + 32 * u;
-      if (c >= chunks) break;
-      float wf[kSkRows][8];
+      const int c = (p0 + u * kSkWarps) * 4 + j;
+      const bool in = c < chunks;
 #pragma unroll
-      for (int r = 0; r < kSkRows; ++r) unpack_bf16x8(raw[r][u], wf[r]);
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        if (m < M) {
-          float xf[8];
-          unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(a + (size_t)m * lda) + c), xf);
-#pragma unroll
-          for (int r = 0; r < kSkRows; ++r)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[m][r] = fmaf(xf[i], wf[r][i], acc[m][r]);
-        }
+      for (int t = 0; t < NT; ++t) {
+        const uint4 x = (in && a_ok[t]) ? __ldg(a_row[t] + c) : zero;
+        const uint32_t a0[4] = {lo[u].x, hi[u].x, lo[u].y, hi[u].y};
+        const uint32_t a1[4] = {lo[u].z, hi[u].z, lo[u].w, hi[u].w};
+        mma_16816(acc[t], a0, x.x, x.y);
+        mma_16816(acc[t], a1, x.z, x.w);
       }
     }
   }
 #pragma unroll
-  for (int m = 0; m < MT; ++m)
+  for (int t = 0; t < NT; ++t)
 #pragma unroll
-    for (int r = 0; r < kSkRows; ++r) acc[m][r] = warp_sum(acc[m][r]);
-  if (lane == 0) {
+    for (int i = 0; i < 4; ++i) red[warp][t][lane][i] = acc[t][i];
+  __syncthreads();
+  // Accumulator layout: values 0, 1 belong to w row r, values 2, 3 to row r + 8; `a` rows 2j, 2j + 1.
+  for (int idx = threadIdx.x; idx < NT * 32 * 4; idx += kSkWarps * 32) {
+    const int t = idx / 128, l = (idx / 4) % 32, i = idx % 4;
+    float sum = 0.f;
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      if (m >= M) break;
-#pragma unroll
-      for (int r = 0; r < kSkRows; ++r) {
-        if (n0 + r < N) {
-          if (OUT_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n0 + r] = acc[m][r];
-          else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n0 + r] = __float2bfloat16_rn(acc[m][r]);
-        }
-      }
+    for (int wv = 0; wv < kSkWarps; ++wv) sum += red[wv][t][l][i];
+    const int n = n0 + (l >> 2) + ((i >> 1) << 3);
+    const int m = t * 8 + (l & 3) * 2 + (i & 1);
+    if (n < N && m < M) {
+      if (OUT_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = sum;
+      else reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(sum);
     }
   }
 }
 
-template <int MT>
+template <int NT>
 int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw, int ldo,
                   int out_f32, cudaStream_t s) {
-  const int rows_per_block = kSkWarps * kSkRows;
-  const unsigned blocks = (unsigned)((N + rows_per_block - 1) / rows_per_block);
+  const unsigned blocks = (unsigned)((N + 15) / 16);
   if (out_f32)
-    linear_skinny_kernel<MT, true><<<blocks, kSkWarps * 32, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+    linear_skinny_kernel<NT, true><<<blocks, kSkWarps * 32, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
                                                                      out, M, N, K, lda, ldw, ldo);
   else
-    linear_skinny_kernel<MT, false><<<blocks, kSkWarps * 32, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+    linear_skinny_kernel<NT, false><<<blocks, kSkWarps * 32, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
                                                                       out, M, N, K, lda, ldw, ldo);
   return check_launch("linear_skinny");
 }
 
 }  // namespace
 
-// Same result contract as erb_linear (no accumulate), for 1 <= M <= 16 with K, lda and ldw
+// Same result contract as erb_linear (no accumulate), for 1 <= M <= 64 with K, lda and ldw
 // multiples of 8 elements and 16-byte aligned operands.
 ERB_EXPORT int erb_linear_skinny(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw,
                                  int ldo, int out_f32, void* stream) {
   if (M <= 0) return ERB_OK;
-  if (M > 16) return fail(ERB_ERR_UNSUPPORTED, "linear_skinny: %d rows (at most 16)", M);
+  if (M > 64) return fail(ERB_ERR_UNSUPPORTED, "linear_skinny: %d rows (at most 64)", M);
   if (N <= 0 || K <= 0 || lda < K || ldw < K || ldo < N) return fail(ERB_ERR_ARG, "linear_skinny: bad sizes");
   if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15))
     return fail(ERB_ERR_UNSUPPORTED, "linear_skinny: K and the leading dimensions must be multiples of 8");
   cudaStream_t s = (cudaStream_t)stream;
-  if (M <= 2) return launch_skinny<2>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
-  if (M <= 4) return launch_skinny<4>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
-  if (M <= 8) return launch_skinny<8>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
-  return launch_skinny<16>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+  if (M <= 8) return launch_skinny<1>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+  if (M <= 16) return launch_skinny<2>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+  if (M <= 32) return launch_skinny<4>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+  return launch_skinny<8>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
 }
 #endif  // ERB_ELEM == 1

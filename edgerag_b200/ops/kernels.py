@@ -33,6 +33,7 @@ _SIGNATURES = {
     "erb_gather_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "erb_linear": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_void_p, c_longlong, c_void_p],
+    "erb_linear_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_attention_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "erb_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -52,6 +53,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
 _LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 2, "erb_linear": 0}
+SKINNY_MAX_ROWS = 64
 
 
 def _fn(library: str, elem: str | None, name: str):
@@ -221,10 +223,17 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate:
         raise KernelError("linear: out must be float32 or the input type")
     if m == 0:
         return
+    lda = a.stride(0) if m > 1 else max(k, a.stride(0))
+    ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
+    if (m <= SKINNY_MAX_ROWS and a.dtype == torch.bfloat16 and not accumulate and k % 8 == 0 and lda % 8 == 0
+            and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+        # a handful of rows: this package's weight-streaming kernel instead of the library product
+        _call(_fn("gemm", "bfloat16", "erb_linear_skinny"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+              lda, k, ldo, int(out.dtype == torch.float32), _stream())
+        return
     ws = _workspace(a.device)
     _call(_fn("gemm", _elem(a), "erb_linear"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
-          a.stride(0) if m > 1 else max(k, a.stride(0)), k, out.stride(0) if m > 1 else max(n, out.stride(0)),
-          int(out.dtype == torch.float32), int(accumulate), ws.data_ptr(), ws.numel(), _stream())
+          lda, k, ldo, int(out.dtype == torch.float32), int(accumulate), ws.data_ptr(), ws.numel(), _stream())
 
 
 # --- attention -------------------------------------------------------------------------------

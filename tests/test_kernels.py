@@ -118,11 +118,15 @@ def test_rope_cache_write(k, dtype, rot):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu_and_residual_and_gather(k, dtype):
+    for inter in (304, 300, 150):          # widths that take the 16-byte path, and ones that do not
+        gu = rand((5, 2 * inter), dtype, 6, 2.0)
+        out = torch.full((5, inter), float("nan"), dtype=dtype, device="cuda")
+        k.swiglu(gu, out)
+        want = torch.nn.functional.silu(gu[:, :inter].float()) * gu[:, inter:].float()
+        torch.testing.assert_close(out.float(), want, **tol(dtype))
     gu = rand((5, 2 * 300), dtype, 6, 2.0)
     out = torch.empty((5, 300), dtype=dtype, device="cuda")
     k.swiglu(gu, out)
-    want = torch.nn.functional.silu(gu[:, :300].float()) * gu[:, 300:].float()
-    torch.testing.assert_close(out.float(), want, **tol(dtype))
     h = rand((5, 300), torch.float32, 7)
     h0 = h.clone()
     k.residual_add(h, out)
@@ -134,7 +138,7 @@ def test_swiglu_and_residual_and_gather(k, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m", [1, 7, 130])
+@pytest.mark.parametrize("m", [1, 7, 16, 33, 64, 130])
 def test_linear(k, dtype, m):
     n, kk = 133, 72
     a, w = rand((m, kk), dtype, 8), rand((n, kk), dtype, 9)
@@ -157,6 +161,26 @@ def test_linear(k, dtype, m):
     assert float(wide_out[:, n:].abs().max()) == 0
     k.linear(a, w, out32, accumulate=True)
     torch.testing.assert_close(out32.double(), 2 * want, atol=2e-4 if dtype == torch.float32 else 4e-3, rtol=1e-5)
+
+
+def test_linear_for_few_rows_streams_weights(k):
+    """Up to 64 bfloat16 rows go through this package's own kernel (16 rows of w per block, any N,
+    K a multiple of 8 but not of a pass); more rows, or float32, through the library."""
+    for m, n, kk in ((8, 49155 // 7, 2048), (3, 50, 8), (16, 257, 1032), (5, 2048, 8192), (64, 100, 72), (29, 31, 264)):
+        a, w = rand((m, kk), torch.bfloat16, 40 + m, 0.5), rand((n, kk), torch.bfloat16, 41 + m, 0.5)
+        want = a.double() @ w.double().T
+        before = dict(k.launch_counts)
+        out = torch.empty((m, n + 3), dtype=torch.float32, device="cuda")[:, :n]
+        k.linear(a, w, out)
+        assert k.launch_counts["own"] == before["own"] + 1 and k.launch_counts["library"] == before["library"]
+        torch.testing.assert_close(out.double(), want, atol=2e-3 * (kk ** 0.5) / 8, rtol=1e-4)
+        out16 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        k.linear(a, w, out16)
+        assert torch.equal(out16, out.bfloat16())          # same sums, rounded once
+    a, w = rand((65, 64), torch.bfloat16, 1), rand((9, 64), torch.bfloat16, 2)
+    before = dict(k.launch_counts)
+    k.linear(a, w, torch.empty((65, 9), dtype=torch.bfloat16, device="cuda"))
+    assert k.launch_counts["library"] == before["library"] + 1
 
 
 # --- attention -------------------------------------------------------------------------------
