@@ -280,6 +280,66 @@ def run_ours(args) -> dict:
     }
 
 
+CONFIG_256M = dict(CONFIG_2B, num_hidden_layers=30, hidden_size=576, num_attention_heads=9, num_key_value_heads=3,
+                   intermediate_size=1536, vocab_size=49280, rope_theta=100000.0)
+CONFIG_500M = dict(CONFIG_2B, num_hidden_layers=32, hidden_size=960, num_attention_heads=15, num_key_value_heads=5,
+                   intermediate_size=2560, vocab_size=49280, rope_theta=100000.0)
+
+
+def run_serving_workload(args) -> dict:
+    """The two serving workloads of the smaller SmolVLM decoders, through ``Engine.generate``:
+
+    * ``mixed``: 256M sizes, 32 requests with prompts of 64..4096 tokens, half of them given as
+      ``prompt_embeds``, 512-token portions beside decode tokens, 64 new tokens each;
+    * ``continuous``: 500M sizes, 64 requests of 7,472 prompt tokens and 128 new tokens, the page
+      pool sized to 80 % of the free memory.
+    """
+    import torch
+
+    sys.path.insert(0, str(ROOT))
+    from edgerag_b200.engine.engine import Engine, EngineOptions
+    from edgerag_b200.sampling.params import SamplingParams
+
+    torch.cuda.set_device(0)
+    gen = torch.Generator().manual_seed(0)
+    if args.workload == "mixed":
+        cfg, n_req, new = CONFIG_256M, 32, 64
+        lens = torch.randint(64, 4097, (n_req,), generator=gen).tolist()
+        options = EngineOptions(dtype="bfloat16", block_size=16, kv_fraction=0.5, max_batch_size=32, chunk_size=512,
+                                max_prefills_per_step=2)
+    else:
+        cfg, n_req, new = CONFIG_500M, 64, 128
+        lens = [7472] * n_req
+        options = EngineOptions(dtype="bfloat16", block_size=16, kv_fraction=0.8, max_batch_size=64, chunk_size=512,
+                                max_prefills_per_step=2)
+    engine = Engine.from_config(cfg, weights_seed=0, std=0.02, options=options)
+    prompts, embeds = [], []
+    for i, n in enumerate(lens):
+        prompts.append(torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist())
+        use_rows = args.workload == "mixed" and i % 2 == 1
+        embeds.append(torch.randn((n, cfg["hidden_size"]), generator=gen).to(torch.bfloat16).cuda() if use_rows else None)
+    warm = engine.generate([prompts[0][:600]], SamplingParams(max_new_tokens=4))   # compiles, sizes buffers
+    assert len(warm[0]) == 4
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    with ClockSampler() as clocks:
+        outs = engine.generate(prompts, SamplingParams(max_new_tokens=new), prompt_embeds=embeds)
+        torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    generated = sum(len(o) for o in outs)
+    stats = engine.scheduler.stats.to_dict()
+    return {
+        "metric": f"{args.workload}_serving_tokens_per_s", "value": round((sum(lens) + generated) / wall, 1),
+        "unit": "tokens/s (prompt + generated)", "generated_tokens_per_s": round(generated / wall, 1), "wall_s": round(wall, 3),
+        "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "higher_is_better": True,
+        "config": {"model": "SmolVLM-256M decoder" if args.workload == "mixed" else "SmolVLM-500M decoder",
+                   "requests": n_req, "prompt_tokens": sum(lens), "new_tokens_each": new, "chunk": 512,
+                   "pool_pages": engine.cache.pages[0].capacity, "page_tokens": 16,
+                   "embeds_requests": sum(e is not None for e in embeds)},
+        "scheduler": stats, "clocks": clocks.record(),
+    }
+
+
 def run_reference(args) -> dict:
     """The unmodified reference: its decoder, paged cache, scheduler and executor, random weights, float16."""
     ref = ROOT / "baseline" / "_ref"
@@ -296,13 +356,18 @@ def run_reference(args) -> dict:
         from edgerag.serve.executor import ModelExecutor
     except Exception as exc:  # the package does not import here
         return {"impl": "reference", "unavailable": f"reference import failed: {type(exc).__name__}: {exc}"[:200]}
-    if not torch.cuda.is_available():
+    on_cpu = bool(getattr(args, "ref_cpu_check", False))    # a small dry run of this function on the CPU
+    if not on_cpu and not torch.cuda.is_available():
         return {"impl": "reference", "unavailable": "no CUDA device"}
 
-    c = CONFIG_2B
+    c = dict(CONFIG_2B)
+    if on_cpu:
+        c.update(hidden_size=64, num_attention_heads=4, num_key_value_heads=4, head_dim=16, intermediate_size=128,
+                 vocab_size=300)
     context, batch, block = args.context, args.batch, 16
     k, w = args.steps, args.warmup
-    device = torch.device("cuda:0")
+    device = torch.device("cpu" if on_cpu else "cuda:0")
+    ref_dtype = torch.float32 if on_cpu else torch.float16
     spec = ModelSpec(
         model_id="bench-2.2b", model_type="smolvlm", n_layers=args.layers, hidden_size=c["hidden_size"],
         n_q_heads=c["num_attention_heads"], n_kv_heads=c["num_key_value_heads"], head_dim=c["head_dim"],
@@ -311,19 +376,27 @@ def run_reference(args) -> dict:
         rms_norm_eps=c["rms_norm_eps"], intermediate_size=c["intermediate_size"], hidden_act="silu")
     torch.manual_seed(0)
     with torch.device(device):
-        decoder = EdgeRagDecoder(spec).eval().to(torch.float16)
+        decoder = EdgeRagDecoder(spec).eval().to(ref_dtype)
     for p in decoder.parameters():
         if p.dim() > 1:
             p.data.normal_(0.0, 0.02)
     allocator = BlockAllocator(batch * (context // block + 2) + 8, block)
-    executor = ModelExecutor(decoder, spec, allocator, device, torch.float16, chunk_size=512)
+    executor = ModelExecutor(decoder, spec, allocator, device, ref_dtype, chunk_size=512)
     scheduler = Scheduler(allocator, SchedulerConfig(max_batch_size=batch, prefill_chunk_size=512,
                                                      cow_reserve_blocks=4, max_prefills_per_step=1))
     gen = torch.Generator().manual_seed(0)
-    new_tokens = k + w + 2
-    prompt_len = context - (2 * (k + w) + 4)
-    requests = [Request(request_id=f"d{i}", prompt_token_ids=torch.randint(0, c["vocab_size"], (prompt_len,), generator=gen).tolist(),
-                        max_new_tokens=new_tokens) for i in range(batch)]
+    # The reference admits one prompt per step and decodes the earlier requests meanwhile, so request i
+    # has generated about chunks * (batch - 1 - i) tokens when the last prompt is in.  Prompts are
+    # shortened by that much, so that every request is near the full context in the timed steps and
+    # none runs out of new tokens before them.
+    chunks = -(-context // 512)
+    requests = []
+    for i in range(batch):
+        ahead = chunks * (batch - 1 - i)
+        new_tokens = ahead + k + w + 4
+        prompt_len = context - new_tokens
+        requests.append(Request(request_id=f"d{i}", max_new_tokens=new_tokens + 64,
+                                prompt_token_ids=torch.randint(0, c["vocab_size"], (prompt_len,), generator=gen).tolist()))
     for r in requests:
         scheduler.add_request(r)
 
@@ -342,26 +415,36 @@ def run_reference(args) -> dict:
         scheduler.end_step()
         return made
 
-    while not all(r.state is RequestState.DECODING for r in requests):
+    for _ in range(chunks * batch + 64):
+        if all(r.state is RequestState.DECODING for r in requests):
+            break
         one_step()
+    else:
+        return {"impl": "reference", "unavailable": "the reference's requests did not all reach decoding"}
     for _ in range(w):
         one_step()
-    torch.cuda.synchronize()
+    sync = (lambda: None) if on_cpu else torch.cuda.synchronize
+    sync()
     clocks = ClockSampler()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if not on_cpu:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with clocks:
         t0 = time.perf_counter()
-        start.record()
+        if not on_cpu:
+            start.record()
         made = 0
         for _ in range(k):
             made += one_step()
-        stop.record()
-        torch.cuda.synchronize()
+        if not on_cpu:
+            stop.record()
+        sync()
         wall = time.perf_counter() - t0
-    ms = start.elapsed_time(stop) / k
+    ms = 1e3 * wall / k if on_cpu else start.elapsed_time(stop) / k
     nums = model_numbers(c, args.layers)
     peak, peak_source = peaks()
-    need = decode_bytes(nums, [context - k - w] * batch)
+    if made != batch * k:
+        return {"impl": "reference", "unavailable": f"only {made} of {batch * k} tokens were decoded in the timed steps"}
+    need = decode_bytes(nums, [r.total_tokens for r in requests])
     achieved = need / (ms / 1e3) / 1e9
     return {
         "metric": "decode_tokens_per_s", "value": round(made / (ms * k / 1e3), 1), "unit": "tokens/s", "n_gpus": 1,
@@ -390,13 +473,23 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=CONFIG_2B["num_hidden_layers"],
                     help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--workload", choices=["decode", "mixed", "continuous"], default="decode",
+                    help="decode: the headline measurement; mixed / continuous: the serving workloads of the "
+                         "256M and 500M decoders through Engine.generate")
+    ap.add_argument("--ref-cpu-check", action="store_true",
+                    help="with --impl reference: a dry run of the reference arm's loop at toy sizes on the CPU")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (nothing here uses more than one GPU)")
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        result = run_reference(args)
+    elif args.workload != "decode":
+        result = run_serving_workload(args)
+    else:
+        result = run_ours(args)
     print(json.dumps(result))
     return 0
 

@@ -25,6 +25,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from .allocator import AllocatorError, OutOfPagesError, UnitAllocator
 
 NO_PAGE = -1
@@ -73,6 +75,25 @@ class BlockTable:
 
     pages: list[int] = field(default_factory=list)
     first_live: int = 0  # index of the first page not yet given back
+    #: the same ids as an int32 array (capacity grows by doubling), for building batches without Python loops
+    _array: np.ndarray = field(default_factory=lambda: np.zeros(16, np.int32), repr=False, compare=False)
+
+    def extend(self, new_pages: list[int]) -> None:
+        n = len(self.pages)
+        if n + len(new_pages) > self._array.size:
+            grown = np.zeros(max(2 * self._array.size, n + len(new_pages)), np.int32)
+            grown[:n] = self._array[:n]
+            self._array = grown
+        self._array[n: n + len(new_pages)] = new_pages
+        self.pages.extend(new_pages)
+
+    def mark_released(self, index: int) -> None:
+        self.pages[index] = NO_PAGE
+        self._array[index] = NO_PAGE
+
+    def array(self) -> np.ndarray:
+        """Page ids as int32 (a view: do not write)."""
+        return self._array[: len(self.pages)]
 
 
 @dataclass
@@ -133,7 +154,7 @@ class CacheManager:
 
     def held_pages(self, request_id: object) -> list[int]:
         rc = self.requests[request_id]
-        return [sum(1 for p in t.pages if p != NO_PAGE) for t in rc.tables]
+        return [len(t.pages) - t.first_live for t in rc.tables]   # released pages are exactly the first ones
 
     # --- life of a request ------------------------------------------------------------------------
 
@@ -166,21 +187,19 @@ class CacheManager:
                 raise OutOfPagesError(
                     f"request {request_id!r} needs {n} more pages, {a.num_free} of {a.capacity} free")
         for n, a, t in zip(extra, self.pages, rc.tables):
-            t.pages.extend(a.allocate(n))
+            t.extend(a.allocate(n))
 
-    def slots_for(self, request_id: object, n_new: int) -> list[list[int]]:
+    def slots_for(self, request_id: object, n_new: int) -> list[np.ndarray]:
         """Per group, the flat cache slot ``page * page_size + offset`` of each of the next ``n_new`` tokens."""
         rc = self.requests[request_id]
         ps = self.page_size
+        positions = np.arange(rc.num_tokens, rc.num_tokens + n_new, dtype=np.int64)
         out = []
         for t in rc.tables:
-            row = []
-            for p in range(rc.num_tokens, rc.num_tokens + n_new):
-                page = t.pages[p // ps]
-                if page == NO_PAGE:
-                    raise AllocatorError(f"request {request_id!r}: position {p} lies in a released page")
-                row.append(page * ps + p % ps)
-            out.append(row)
+            pages = t.array()[positions // ps]
+            if (pages == NO_PAGE).any():
+                raise AllocatorError(f"request {request_id!r}: a position to write lies in a released page")
+            out.append((pages.astype(np.int64) * ps + positions % ps).astype(np.int32))
         return out
 
     def advance(self, request_id: object, n_new: int) -> None:
@@ -201,7 +220,7 @@ class CacheManager:
                 page = t.pages[t.first_live]
                 self.pages[gi].free([page])
                 self._freed.append((gi, page))
-                t.pages[t.first_live] = NO_PAGE
+                t.mark_released(t.first_live)
                 t.first_live += 1
 
     def release(self, request_id: object) -> None:

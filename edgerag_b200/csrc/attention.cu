@@ -117,6 +117,7 @@ attention_rows_kernel(const T* __restrict__ q, int q_row_stride, const T* __rest
                       const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                       T* __restrict__ out, int out_row_stride, int n_tokens, int nq, int nkv,
                       int page_size, int window, float scale) {
+  chain_wait();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* q_s = smem + warp * D;
@@ -168,6 +169,7 @@ attention_decode_split_kernel(const T* __restrict__ q, int q_row_stride, const T
                               const int* __restrict__ positions, float* __restrict__ part_acc,
                               float* __restrict__ part_ml, int max_splits, int nq, int nkv, int page_size,
                               int window, int split_keys, float scale) {
+  chain_wait();
   extern __shared__ float smem[];
   float* q_s = smem;                                   // D
   float* stage = smem + D;                             // kDecodeWarps * 32 * (D + 1)
@@ -241,6 +243,7 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_a
                                                 const int* __restrict__ positions, T* __restrict__ out,
                                                 int out_row_stride, int max_splits, int nq, int head_dim,
                                                 int window, int split_keys) {
+  chain_wait();
   const int h = blockIdx.x, seq = blockIdx.y;
   const int t = token_of_seq[seq];
   const int pos = positions[t];
@@ -273,7 +276,7 @@ int launch_rows(const void* q, int q_row_stride, const void* k_pages, const void
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_rows: %s", cudaGetErrorString(e));
   }
   dim3 grid((n_tokens + kRowWarps - 1) / kRowWarps, nq);
-  kern<<<grid, kRowWarps * 32, smem, s>>>((const T*)q, q_row_stride, (const T*)k_pages, (const T*)v_pages,
+  launch_chained(kern, dim3(grid), dim3(kRowWarps * 32), smem, s, (const T*)q, q_row_stride, (const T*)k_pages, (const T*)v_pages,
       block_tables, max_pages, seq_of_token, positions, (T*)out, out_row_stride, n_tokens, nq, nkv,
       page_size, window, scale);
   return check_launch("attention_rows");
@@ -292,12 +295,12 @@ int launch_decode(const void* q, int q_row_stride, const void* k_pages, const vo
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_decode: %s", cudaGetErrorString(e));
   }
   dim3 grid(max_splits, nq, n_seqs);
-  kern<<<grid, kDecodeWarps * 32, smem, s>>>((const T*)q, q_row_stride, (const T*)k_pages,
+  launch_chained(kern, dim3(grid), dim3(kDecodeWarps * 32), smem, s, (const T*)q, q_row_stride, (const T*)k_pages,
       (const T*)v_pages, block_tables, max_pages, token_of_seq, positions, part_acc, part_ml, max_splits,
       nq, nkv, page_size, window, split_keys, scale);
   int rc = check_launch("attention_decode_split");
   if (rc) return rc;
-  attention_decode_combine_kernel<T><<<dim3(nq, n_seqs), 64, 0, s>>>(part_acc, part_ml, token_of_seq,
+  launch_chained(attention_decode_combine_kernel<T>, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq,
       positions, (T*)out, out_row_stride, max_splits, nq, D, window, split_keys);
   return check_launch("attention_decode_combine");
 }

@@ -3,17 +3,16 @@
 // bfloat16, head size 64, queries of one (sequence, query head) in tiles of 128 rows, keys and
 // values read straight from cache pages in tiles of 128 keys.
 //
-//   S = Q K^T      tcgen05.mma  M=128 N=128 K=16 x4   A = Q tile, B = K tile, both K-major in
+//   S = Q K^T      tcgen05.mma  M=128 N=64 K=16 x4    A = Q tile, B = K tile, both K-major in
 //                  shared memory (rows of 128 bytes, 128-byte swizzle), accumulator in TMEM
-//   softmax        each of the 128 threads owns one query row: tcgen05.ld of its S row, running
-//                  max / denominator in float, P rounded to bfloat16 and written to shared memory
-//   O += P V       tcgen05.mma  M=128 N=64 K=16 x8    A = P (K-major), B = V tile as stored in the
-//                  cache (rows = keys, 64 contiguous values: the MN-major operand form)
+//   softmax        two threads per query row, 32 score columns each: tcgen05.ld of their part of the
+//                  S row, reference max / denominator in float, P rounded to bfloat16 into shared memory
+//   O += P V       tcgen05.mma  M=128 N=64 K=16 x4    A = P (K-major), B = V tile as stored in the
+//                  cache (rows = keys, 64 contiguous values: the MN-major operand form); O stays in TMEM
 //
-// K and V tiles are brought in with cp.async 16-byte copies (zero-filled past the last visible
-// key), double buffered: tile j+1 is in flight while tile j is multiplied.  One block is 128
-// threads and 113 KB of shared memory, so two blocks share an SM and overlap each other's
-// copy, multiply and softmax phases; each allocates 256 TMEM columns.
+// K and V tiles of 64 keys are brought in with cp.async 16-byte copies (zero-filled past the last
+// visible key), two tiles ahead, four stages.  One block is 256 threads and 113 KB of shared
+// memory, so two blocks (16 warps) share an SM; each allocates 256 TMEM columns.
 //
 // Every wait on an mbarrier is bounded: on a timeout the block records an error in *status,
 // skips the rest of its work, frees its TMEM and returns.
@@ -34,13 +33,17 @@ ERB_DEFINE_LAST_ERROR(erb_last_error)
 namespace {
 
 constexpr int BM = 128;       // query rows per block
-constexpr int BN = 128;       // keys per tile
+constexpr int BN = 64;        // keys per tile
 constexpr int HD = 64;        // head size
-constexpr int kThreads = 128;
-constexpr uint32_t kTileBytes = BN * HD * 2;        // 16 KB: one K or V tile, or the Q tile
-constexpr uint32_t kPBytes = BM * BN * 2;           // 32 KB: P, two 64-key halves of 16 KB
-constexpr uint32_t kSmemBytes = kTileBytes /*Q*/ + 4 * kTileBytes /*K,V x2*/ + kPBytes + 1024 /*align*/ + 64;
-constexpr uint32_t kTmemCols = 256;                 // S: columns 0..127, P*V: columns 128..191
+constexpr int kThreads = 256;     // two threads per query row
+constexpr int kKvStages = 4;      // K and V tiles in shared memory
+constexpr uint32_t kQBytes = BM * HD * 2;           // 16 KB: the Q tile
+constexpr uint32_t kTileBytes = BN * HD * 2;        // 8 KB: one K or V tile
+constexpr uint32_t kPBytes = BM * BN * 2;           // 16 KB: one P tile (two of them)
+// 114,752 bytes of tiles + 64 of barriers: two blocks fit in an SM's 227 KB (each block also costs 1 KB of
+// system shared memory), which needs the dynamic shared memory to start 1024-byte aligned: checked at run time.
+constexpr uint32_t kSmemBytes = kQBytes + 2 * kKvStages * kTileBytes + 2 * kPBytes + 64;
+constexpr uint32_t kTmemCols = 256;                 // S(even tiles): columns 0..63, S(odd): 64..127, O: 128..191
 constexpr uint32_t kSpinLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -119,26 +122,58 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
-__global__ void __launch_bounds__(kThreads)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Pipeline (one block, tile j of 64 keys):
+//   copies for tile j+2 are in flight (cp.async, four stages);
+//   S(j+1) = Q K(j+1)^T is issued before the softmax of tile j, into the other half of the S columns;
+//   the softmax of tile j reads S(j) from TMEM, writes P(j) (bfloat16) to one of two shared buffers;
+//   O += P(j) V(j) accumulates in TMEM and is only waited for when its inputs are reused two tiles
+//   later, or when the running maximum of a row grew by more than 2^8 and O must be rescaled.
+// The softmax keeps a reference maximum per row that only moves in such jumps (p <= 2^8 in between), so
+// the O rescale, the one step that would serialise the tensor core behind the CUDA cores, is rare.
+__global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
                             const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                             const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
                             const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, int out_row_stride,
                             int n_seqs, int nq, int nkv, int page_size, float scale_log2, int* __restrict__ status) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* smem = smem_raw + (base - raw);
-  const uint32_t sQ = base, sK0 = base + kTileBytes, sV0 = sK0 + 2 * kTileBytes, sP = sV0 + 2 * kTileBytes;
-  const uint32_t bar_s = sP + kPBytes, bar_o = bar_s + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_s - base) + 16);
+  chain_wait();
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {                       // the swizzled tiles need 1024-byte aligned bases
+    if (threadIdx.x == 0) atomicCAS(status, 0, 3000000);
+    return;
+  }
+  uint8_t* smem = smem_raw;
+  const uint32_t sQ = base, sK0 = base + kQBytes, sV0 = sK0 + kKvStages * kTileBytes, sP0 = sV0 + kKvStages * kTileBytes;
+  const uint32_t bar0 = sP0 + 2 * kPBytes;          // bar_s[0], bar_s[1], bar_pv[0], bar_pv[1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar0 - base) + 32);
 
+  // Two threads per query row: thread (row, half) owns score columns half*32 .. +31 of a tile and
+  // output columns half*32 .. +31.  A warp reaches the 32 TMEM lanes of its quarter.
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = tid & (BM - 1), half = tid >> 7;
   const int h = blockIdx.y;
   const int kvh = h / (nq / nkv);
 
-  // Which sequence and which 128-row tile of it this block owns.
-  int tile = blockIdx.x, seq = -1, q0 = 0, rows = 0;
+  // Which sequence and which 128-row tile of it this block owns.  Blocks are numbered from the last
+  // tile backwards: later tiles of a prompt see more keys and take longer, so they should start first.
+  int tile = (int)(gridDim.x - 1 - blockIdx.x), seq = -1, q0 = 0, rows = 0;
   for (int s = 0; s < n_seqs; ++s) {
     const int begin = seq_starts[s], len = seq_starts[s + 1] - begin;
     const int n_tiles = (len + BM - 1) / BM;
@@ -149,12 +184,12 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
   if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier block gave up: do not pile on
   const int pos0 = positions[q0];
   const int last_key = pos0 + rows - 1;
-  const int n_kv_tiles = last_key / BN + 1;
+  const int n_kv = last_key / BN + 1;
   const int* bt = block_tables + (size_t)seq * max_pages;
 
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_o));
+#pragma unroll
+    for (int b = 0; b < 4; ++b) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8 * b));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -164,161 +199,178 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
 
-  // Each thread copies chunk (tid % 8) of rows (tid / 8) + 16 i, so a warp covers whole 128-byte rows.
+  // Each thread copies chunk (tid % 8) of rows (tid / 8) + 32 i, so a warp covers whole 128-byte rows.
   const int lc = tid & 7, lr = tid >> 3;
-  auto load_kv = [&](int j, int stage) {
-    const uint32_t dK = sK0 + stage * kTileBytes, dV = sV0 + stage * kTileBytes;
+  auto load_kv = [&](int j) {               // always commits a group, empty past the last tile
+    if (j < n_kv) {
+      const int stage = j % kKvStages;
+      const uint32_t dK = sK0 + stage * kTileBytes, dV = sV0 + stage * kTileBytes;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = lr + 16 * i;
-      const int key = j * BN + r;
-      const bool valid = key <= last_key;
-      size_t off = 0;
-      if (valid) {
-        const int page = bt[key / page_size];
-        off = (((size_t)page * nkv + kvh) * page_size + (key % page_size)) * HD + lc * 8;
+      for (int i = 0; i < BN / 32; ++i) {
+        const int r = lr + 32 * i;
+        const int key = j * BN + r;
+        const bool valid = key <= last_key;
+        size_t off = 0;
+        if (valid) {
+          const int page = bt[key / page_size];
+          off = (((size_t)page * nkv + kvh) * page_size + (key % page_size)) * HD + lc * 8;
+        }
+        cp_async16(dK + swz(r, lc), k_pages + off, valid);
+        cp_async16(dV + swz(r, lc), v_pages + off, valid);
       }
-      cp_async16(dK + swz(r, lc), k_pages + off, valid);
-      cp_async16(dV + swz(r, lc), v_pages + off, valid);
     }
     cp_async_commit();
   };
 
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int r = lr + 16 * i;
+  for (int i = 0; i < BM / 32; ++i) {
+    const int r = lr + 32 * i;
     const bool valid = r < rows;
     const __nv_bfloat16* src = q + (size_t)(q0 + (valid ? r : 0)) * q_row_stride + (size_t)h * HD + lc * 8;
     cp_async16(sQ + swz(r, lc), src, valid);
   }
-  load_kv(0, 0);
-
+  load_kv(0);
+  load_kv(1);
+  cp_async_wait<1>();                       // Q and tile 0 have landed
+  fence_async_proxy();
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes of TMEM
-  const int my_pos = pos0 + tid;
-
-  float o[HD];
-#pragma unroll
-  for (int d = 0; d < HD; ++d) o[d] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
+  const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes of TMEM
+  const uint32_t t_o = t_lane + 2 * BN + half * 32;                      // this thread's 32 output columns
+  const int my_pos = pos0 + row;
+  const uint64_t dq = make_desc(sQ);
   bool ok = true;
 
-  for (int j = 0; j < n_kv_tiles; ++j) {
-    const int stage = j & 1;
-    cp_async_wait_all();
-    fence_async_proxy();
-    __syncthreads();                       // tile j (and Q) are in shared memory for everyone
-    if (j + 1 < n_kv_tiles) load_kv(j + 1, stage ^ 1);
-
-    if (tid == 0 && ok) {
-      fence_after_sync();
-      const uint64_t dq = make_desc(sQ), dk = make_desc(sK0 + stage * kTileBytes);
+  auto issue_s = [&](int j) {               // thread 0: S(j) into S columns (j & 1) * 64
+    const uint64_t dk = make_desc(sK0 + (j % kKvStages) * kTileBytes);
 #pragma unroll
-      for (int k = 0; k < HD / 16; ++k) mma_bf16(tmem, dq + 2 * k, dk + 2 * k, kIdescS, k > 0);
-      mma_commit(bar_s);
-    }
-    if (ok && !mbar_wait(bar_s, j & 1)) ok = false;
-    fence_after_sync();
+    for (int k = 0; k < HD / 16; ++k) mma_bf16(tmem + (j & 1) * BN, dq + 2 * k, dk + 2 * k, kIdescS, k > 0);
+    mma_commit(bar0 + 8 * (j & 1));
+  };
+  if (tid == 0) issue_s(0);
 
+  float m_ref = -INFINITY, l_run = 0.f;     // l_run: this thread's half of the row's denominator
+  for (int j = 0; j < n_kv; ++j) {
+    // (A) tile j+1 is in shared memory for everyone; everyone is done with iteration j-1
+    cp_async_wait<0>();
+    fence_async_proxy();
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (tid == 0 && ok && j + 1 < n_kv) issue_s(j + 1);
+    // the stage tile j+2 goes into was last read by P V of tile j-2
+    if (ok && j >= 2 && !mbar_wait(bar0 + 16 + 8 * (j & 1), ((j - 2) >> 1) & 1)) ok = false;
+    load_kv(j + 2);
+
+    if (ok && !mbar_wait(bar0 + 8 * (j & 1), (j >> 1) & 1)) ok = false;
+    fence_after_sync();
+    float s[32];
+    if (ok) {
+      tmem_ld32(t_lane + (j & 1) * BN + half * 32, s);
+      tmem_ld_wait();
+    }
+    const int key0 = j * BN + half * 32;
+    float m_half = -INFINITY;
+    if (key0 + 31 <= my_pos) {              // every key of this half is visible to this row
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { s[i] *= scale_log2; m_half = fmaxf(m_half, s[i]); }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        s[i] = (key0 + i <= my_pos) ? s[i] * scale_log2 : -INFINITY;
+        m_half = fmaxf(m_half, s[i]);
+      }
+    }
+    // The two threads of a row exchange their maxima through the P buffer of this tile, which is free
+    // (P V of tile j-2 was waited for above): each writes into the first bytes of its partner's part of
+    // the row and reads its own part, which nobody else touches until the thread overwrites it with P.
+    uint8_t* p_row = smem + (sP0 - base) + (j & 1) * kPBytes;
+    *reinterpret_cast<float*>(p_row + swz(row, (half ^ 1) * 4)) = m_half;
+    __syncthreads();
+    const float m_tile = fmaxf(m_half, *reinterpret_cast<const float*>(p_row + swz(row, half * 4)));
+    // The reference maximum moves only when the row's maximum grew by more than 2^8.
     float alpha = 1.f;
-    if (ok) {
-      // Pass 1: the row's maximum over the visible keys of this tile.
-      const bool diag = (j * BN + BN - 1) > pos0;      // some key of the tile is masked for some row
-      float m_tile = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        float s[32];
-        tmem_ld32(t_row + c * 32, s);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = j * BN + c * 32 + i;
-          if (!diag || key <= my_pos) m_tile = fmaxf(m_tile, s[i]);
-        }
-      }
-      const float m_new = fmaxf(m_run, m_tile);
-      const float ms = (m_new == -INFINITY) ? 0.f : m_new * scale_log2;
-      alpha = exp2f(m_run * scale_log2 - ms);           // 0 on the first tile (m_run = -inf)
-      if (m_run == -INFINITY) alpha = 0.f;
-      float l_tile = 0.f;
-      // Pass 2: probabilities, rounded to bfloat16, into the P tile (two 64-key halves).
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        float s[32];
-        tmem_ld32(t_row + c * 32, s);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int key = j * BN + c * 32 + i;
-          float p0 = (!diag || key <= my_pos) ? exp2f(s[i] * scale_log2 - ms) : 0.f;
-          float p1 = (!diag || key + 1 <= my_pos) ? exp2f(s[i + 1] * scale_log2 - ms) : 0.f;
-          l_tile += p0 + p1;
-          __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-          packed[i / 2] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        const int half = c >> 1;                       // keys 0..63 or 64..127
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = (c & 1) * 4 + g;           // 16-byte chunk inside the half's 128-byte row
-          uint8_t* dst = smem + (sP - base) + half * (BM * 128) + swz(tid, chunk);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
-        }
-      }
-      l_run = l_run * alpha + l_tile;
-      m_run = m_new;
+    const bool jump = m_tile > m_ref + 8.f;               // true on the first tile (m_ref = -inf)
+    if (jump) {
+      alpha = exp2f(m_ref - m_tile);                      // 0 on the first tile
+      m_ref = m_tile;
     }
+    if (j > 0 && __any_sync(0xffffffffu, jump)) {
+      // O of this warp's rows is rescaled in TMEM; P V of tile j-1 must have landed first
+      if (ok && !mbar_wait(bar0 + 16 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1)) ok = false;
+      fence_after_sync();
+      if (ok) {
+        float acc[32];
+        tmem_ld32(t_o, acc);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] *= alpha;
+        tmem_st32(t_o, acc);
+        tmem_st_wait();
+      }
+    }
+    float l_tile = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {           // this thread's four 16-byte chunks of the row of P
+      uint32_t packed[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float p0 = exp2f(s[8 * g + 2 * i] - m_ref), p1 = exp2f(s[8 * g + 2 * i + 1] - m_ref);
+        l_tile += p0 + p1;
+        __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+        packed[i] = *reinterpret_cast<uint32_t*>(&b);
+      }
+      if (ok) *reinterpret_cast<uint4*>(p_row + swz(row, half * 4 + g)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+    l_run = l_run * alpha + l_tile;
     fence_async_proxy();
     fence_before_sync();
-    __syncthreads();                       // P is written and every thread is done reading S
-
+    __syncthreads();                        // (B) P(j) is written, O is rescaled, S(j) has been read
     if (tid == 0 && ok) {
       fence_after_sync();
-      const uint64_t dp = make_desc(sP), dv = make_desc(sV0 + stage * kTileBytes);
+      const uint64_t dp = make_desc(sP0 + (j & 1) * kPBytes), dv = make_desc(sV0 + (j % kKvStages) * kTileBytes);
 #pragma unroll
-      for (int k = 0; k < BN / 16; ++k) {
-        const uint64_t a = dp + (uint64_t)((k >> 2) * (BM * 128 >> 4) + (k & 3) * 2);   // half, then 32 bytes per step
-        const uint64_t b = dv + (uint64_t)(k * (2048 >> 4));                            // 16 keys = 2 groups of 8 rows
-        mma_bf16(tmem + BN, a, b, kIdescO, k > 0);
-      }
-      mma_commit(bar_o);
+      for (int k = 0; k < BN / 16; ++k)
+        mma_bf16(tmem + 2 * BN, dp + 2 * k, dv + (uint64_t)(k * (2048 >> 4)), kIdescO, (j > 0 || k > 0) ? 1u : 0u);
+      mma_commit(bar0 + 16 + 8 * (j & 1));
     }
-    if (ok && !mbar_wait(bar_o, j & 1)) ok = false;
-    fence_after_sync();
-    if (ok) {
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        float pv[32];
-        tmem_ld32(t_row + BN + c * 32, pv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + pv[i];
-      }
-    }
-    fence_before_sync();
   }
-  cp_async_wait_all();
+  cp_async_wait<0>();
+  // every P V has landed once the last two have
+  if (ok && n_kv >= 2 && !mbar_wait(bar0 + 16 + 8 * ((n_kv - 2) & 1), ((n_kv - 2) >> 1) & 1)) ok = false;
+  if (ok && !mbar_wait(bar0 + 16 + 8 * ((n_kv - 1) & 1), ((n_kv - 1) >> 1) & 1)) ok = false;
+  fence_after_sync();
+  // exchange the two halves of the denominator (through P buffer 0: no P V reads it any more)
+  uint8_t* p_row = smem + (sP0 - base);
+  *reinterpret_cast<float*>(p_row + swz(row, (half ^ 1) * 4)) = l_run;
   __syncthreads();
+  const float l_row = l_run + *reinterpret_cast<const float*>(p_row + swz(row, half * 4));
 
   if (!ok) {
     atomicCAS(status, 0, 1000000 + (int)blockIdx.x);
-  } else if (tid < rows) {
-    const float inv = 1.f / l_run;
-    __nv_bfloat16* dst = out + (size_t)(q0 + tid) * out_row_stride + (size_t)h * HD;
+  } else {
+    float acc[32];
+    tmem_ld32(t_o, acc);
+    tmem_ld_wait();
+    if (row < rows) {
+      const float inv = 1.f / l_row;
+      __nv_bfloat16* dst = out + (size_t)(q0 + row) * out_row_stride + (size_t)h * HD + half * (HD / 2);
 #pragma unroll
-    for (int d = 0; d < HD; d += 8) {
-      uint32_t w[4];
+      for (int d = 0; d < HD / 2; d += 8) {
+        uint32_t w[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        __nv_bfloat162 b = __floats2bfloat162_rn(o[d + 2 * i] * inv, o[d + 2 * i + 1] * inv);
-        w[i] = *reinterpret_cast<uint32_t*>(&b);
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 b = __floats2bfloat162_rn(acc[d + 2 * i] * inv, acc[d + 2 * i + 1] * inv);
+          w[i] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
+  fence_before_sync();
+  __syncthreads();
   if (warp == 0) {
     fence_after_sync();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -351,7 +403,7 @@ ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const v
     configured = true;
   }
   const float scale_log2 = scale * 1.4426950408889634f;
-  attention_prefill_tc_kernel<<<dim3(n_tiles, nq), kThreads, kSmemBytes, (cudaStream_t)stream>>>(
+  launch_chained(attention_prefill_tc_kernel, dim3(dim3(n_tiles, nq)), dim3(kThreads), kSmemBytes, (cudaStream_t)stream, 
       (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
       block_tables, max_pages, seq_starts, positions, (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv,
       page_size, scale_log2, status);
@@ -406,6 +458,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
                              float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
                              int nkv, int page_size, int split_keys, float scale_log2, int hg,
                              int* __restrict__ status) {
+  chain_wait();
   // hg: kv heads handled by this block.  The rows of hg neighbouring heads of one page are contiguous
   // in the cache, so a block that takes them together copies hg * page_size rows in one piece; with
   // small pages that is what keeps the copies long enough for the memory system.
@@ -639,6 +692,7 @@ attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const f
                                      const int* __restrict__ token_of_seq, const int* __restrict__ positions,
                                      __nv_bfloat16* __restrict__ out, int out_row_stride, int max_splits,
                                      int nq, int head_dim, int split_keys) {
+  chain_wait();
   __shared__ float s_w[kCombineMaxSplits];
   __shared__ float s_red[2];
   const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
@@ -690,7 +744,7 @@ int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, con
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_decode_bulk: %s", cudaGetErrorString(e));
     configured = smem;
   }
-  kern<<<dim3(max_splits, nkv / hg, n_seqs), kDecThreads, smem, s>>>((const __nv_bfloat16*)q, q_row_stride,
+  launch_chained(kern, dim3(dim3(max_splits, nkv / hg, n_seqs)), dim3(kDecThreads), smem, s, (const __nv_bfloat16*)q, q_row_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, token_of_seq, positions,
       part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, status);
   return check_launch("attention_decode_bulk");
@@ -746,7 +800,7 @@ ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const 
     default: return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: head_dim %d (takes 32, 64, 128)", head_dim);
   }
   if (rc) return rc;
-  attention_decode_bulk_combine_kernel<<<dim3(nq, n_seqs), 64, 0, s>>>(part_acc, part_ml, token_of_seq, positions,
+  launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
       (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
   return check_launch("attention_decode_bulk_combine");
 }

@@ -11,6 +11,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 // Each source is compiled once per element type: -DERB_ELEM=0 (float) or 1 (bfloat16).
 #ifndef ERB_ELEM
@@ -109,6 +110,41 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   float t = (lane < nwarp) ? scratch[lane] : -INFINITY;
   t = warp_max(t);
   return t;
+}
+
+// Chained launches.  Kernels that run back to back in the decode step are launched with
+// programmatic stream serialization: the next kernel's blocks may be scheduled while the previous
+// kernel drains, which hides the launch latency between the many short kernels of a step.  Every
+// such kernel calls chain_wait() before it touches memory, which blocks until the previous kernel
+// has completed and its writes are visible; so the data flow is that of ordinary stream order.
+// EDGERAG_B200_NO_CHAIN=1 in the environment turns the attribute off.
+__device__ __forceinline__ void chain_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+inline bool chain_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("EDGERAG_B200_NO_CHAIN");
+    return !(v && v[0] == '1');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chain_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in check_launch()
 }
 
 }  // namespace erb

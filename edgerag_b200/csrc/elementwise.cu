@@ -18,6 +18,7 @@ __global__ void embed_rows_kernel(float* __restrict__ hidden, const T* __restric
                                   const T* __restrict__ embeds, const int* __restrict__ ids,
                                   const int* __restrict__ embed_row, int hidden_size, int vocab,
                                   int n_embed_rows, int* __restrict__ status) {
+  chain_wait();
   const int t = blockIdx.x;
   const int er = embed_row ? embed_row[t] : -1;
   const T* src = nullptr;
@@ -38,7 +39,7 @@ ERB_EXPORT int erb_embed_rows(void* hidden, const void* table, const void* embed
   if (n_tokens <= 0) return ERB_OK;
   if (hidden_size <= 0 || vocab <= 0) return fail(ERB_ERR_ARG, "embed_rows: bad sizes");
   const int threads = hidden_size >= 1024 ? 256 : 128;
-  embed_rows_kernel<elem_t><<<n_tokens, threads, 0, (cudaStream_t)stream>>>((float*)hidden,
+  launch_chained(embed_rows_kernel<elem_t>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (float*)hidden,
       (const elem_t*)table, (const elem_t*)embeds, ids, embed_row, hidden_size, vocab, n_embed_rows, status);
   return check_launch("embed_rows");
 }
@@ -56,6 +57,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden_size, float eps,
                                    int write_back) {
+  chain_wait();
   extern __shared__ float row_cache[];  // hidden_size floats, then 32 of scratch
   float* scratch = row_cache + hidden_size;
   const int o = blockIdx.x;
@@ -104,6 +106,7 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __r
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
                                         int write_back) {
+  chain_wait();
   extern __shared__ float row_cache[];
   float* scratch = row_cache + hidden_size;
   const int o = blockIdx.x;
@@ -158,10 +161,10 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "add_rmsnorm: %s", cudaGetErrorString(e));
     }
-    add_rmsnorm_vec4_kernel<elem_t><<<n_rows, threads, smem, (cudaStream_t)stream>>>((float*)hidden,
+    launch_chained(add_rmsnorm_vec4_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
         (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
   } else {
-    add_rmsnorm_kernel<elem_t><<<n_rows, threads, smem, (cudaStream_t)stream>>>((float*)hidden,
+    launch_chained(add_rmsnorm_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
         (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
   }
   return check_launch("add_rmsnorm");
@@ -170,6 +173,7 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
 // hidden[row] += delta[row] without a norm (the last residual of a stack that ends without one).
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ hidden, const T* __restrict__ delta, size_t n) {
+  chain_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) hidden[i] += Elem<T>::load(delta + i);
 }
@@ -178,7 +182,7 @@ ERB_EXPORT int erb_residual_add(void* hidden, const void* delta, long long n, vo
   if (n <= 0) return ERB_OK;
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
-  residual_add_kernel<elem_t><<<blocks, threads, 0, (cudaStream_t)stream>>>((float*)hidden,
+  launch_chained(residual_add_kernel<elem_t>, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, (float*)hidden,
       (const elem_t*)delta, (size_t)n);
   return check_launch("residual_add");
 }
@@ -198,6 +202,7 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
                                         const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                         T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
                                         int head_dim, int rot_dim, int page_size, int write_kv) {
+  chain_wait();
   const int t = blockIdx.x;
   const int row_width = (nq + 2 * nkv) * head_dim;
   T* row = qkv + (size_t)t * row_width;
@@ -252,6 +257,7 @@ __global__ void rope_cache_write_vec4_kernel(T* __restrict__ qkv, const int* __r
                                              const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                              T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
                                              int head_dim, int page_size, int write_kv) {
+  chain_wait();
   extern __shared__ float trig[];            // cos[half], sin[half]
   const int t = blockIdx.x;
   const int half = head_dim / 2;
@@ -314,12 +320,12 @@ ERB_EXPORT int erb_rope_cache_write(void* qkv, const int* positions, const float
     const int want = (148 * 8 + n_tokens - 1) / n_tokens;      // enough blocks for every SM
     if (y > want) y = want;
     if (y < 1) y = 1;
-    rope_cache_write_vec4_kernel<elem_t><<<dim3(n_tokens, y), 128, head_dim * sizeof(float), (cudaStream_t)stream>>>(
+    launch_chained(rope_cache_write_vec4_kernel<elem_t>, dim3(dim3(n_tokens, y)), dim3(128), head_dim * sizeof(float), (cudaStream_t)stream, 
         (elem_t*)qkv, positions, inv_freq, slots, (elem_t*)k_pages, (elem_t*)v_pages, nq, nkv, head_dim, page_size,
         write_kv);
     return check_launch("rope_cache_write");
   }
-  rope_cache_write_kernel<elem_t><<<n_tokens, threads, 0, (cudaStream_t)stream>>>((elem_t*)qkv, positions,
+  launch_chained(rope_cache_write_kernel<elem_t>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (elem_t*)qkv, positions,
       inv_freq, slots, (elem_t*)k_pages, (elem_t*)v_pages, nq, nkv, head_dim, rot_dim, page_size, write_kv);
   return check_launch("rope_cache_write");
 }
@@ -329,6 +335,7 @@ ERB_EXPORT int erb_rope_cache_write(void* qkv, const int* positions, const float
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  chain_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / inter;
@@ -356,6 +363,7 @@ template <> struct Vec16<__nv_bfloat16> {
 
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t groups) {
+  chain_wait();
   constexpr int N = Vec16<T>::N;
   const size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gidx >= groups) return;
@@ -378,12 +386,12 @@ ERB_EXPORT int erb_swiglu(const void* gate_up, void* out, int n_tokens, int inte
   const int threads = 256;
   if (inter % Vec16<elem_t>::N == 0 && !((uintptr_t)gate_up & 15) && !((uintptr_t)out & 15)) {
     const size_t groups = total / Vec16<elem_t>::N;
-    swiglu_vec_kernel<elem_t><<<(unsigned)((groups + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
+    launch_chained(swiglu_vec_kernel<elem_t>, dim3((unsigned)((groups + threads - 1) / threads)), dim3(threads), 0, (cudaStream_t)stream, 
         (const elem_t*)gate_up, (elem_t*)out, inter, groups);
     return check_launch("swiglu");
   }
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-  swiglu_kernel<elem_t><<<blocks, threads, 0, (cudaStream_t)stream>>>((const elem_t*)gate_up, (elem_t*)out,
+  launch_chained(swiglu_kernel<elem_t>, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, (const elem_t*)gate_up, (elem_t*)out,
                                                                      inter, total);
   return check_launch("swiglu");
 }
@@ -393,6 +401,7 @@ ERB_EXPORT int erb_swiglu(const void* gate_up, void* out, int n_tokens, int inte
 template <typename T>
 __global__ void gather_cast_kernel(const float* __restrict__ src, T* __restrict__ dst,
                                    const int* __restrict__ rows, int width) {
+  chain_wait();
   const int o = blockIdx.x;
   const float* s = src + (size_t)(rows ? rows[o] : o) * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) Elem<T>::store(dst + (size_t)o * width + i, s[i]);
@@ -401,6 +410,6 @@ __global__ void gather_cast_kernel(const float* __restrict__ src, T* __restrict_
 ERB_EXPORT int erb_gather_cast(const float* src, void* dst, const int* rows, int n_rows, int width,
                                void* stream) {
   if (n_rows <= 0) return ERB_OK;
-  gather_cast_kernel<elem_t><<<n_rows, 256, 0, (cudaStream_t)stream>>>(src, (elem_t*)dst, rows, width);
+  launch_chained(gather_cast_kernel<elem_t>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, src, (elem_t*)dst, rows, width);
   return check_launch("gather_cast");
 }

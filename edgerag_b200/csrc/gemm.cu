@@ -149,6 +149,7 @@ template <int NT, bool OUT_F32>   // NT: tiles of 8 rows of `a`
 __global__ void __launch_bounds__(kSkWarps * 32)
 linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                      int M, int N, int K, int lda, int ldw, int ldo) {
+  chain_wait();
   __shared__ float red[kSkWarps][NT][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
@@ -219,10 +220,10 @@ int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, 
                   int out_f32, cudaStream_t s) {
   const unsigned blocks = (unsigned)((N + 15) / 16);
   if (out_f32)
-    linear_skinny_kernel<NT, true><<<blocks, kSkWarps * 32, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+    launch_chained(linear_skinny_kernel<NT, true>, dim3(blocks), dim3(kSkWarps * 32), 0, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
                                                                      out, M, N, K, lda, ldw, ldo);
   else
-    linear_skinny_kernel<NT, false><<<blocks, kSkWarps * 32, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
+    launch_chained(linear_skinny_kernel<NT, false>, dim3(blocks), dim3(kSkWarps * 32), 0, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
                                                                       out, M, N, K, lda, ldw, ldo);
   return check_launch("linear_skinny");
 }

@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(kThreads)
 sample_rows_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
                    const float* __restrict__ temperature, const long long* __restrict__ rng_state,
                    int* __restrict__ tokens) {
+  chain_wait();
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ float s_scan[kThreads];
@@ -113,7 +114,7 @@ ERB_EXPORT int erb_sample_rows(const float* logits, long long row_stride, int n_
   if (n_rows <= 0) return ERB_OK;
   if (vocab <= 0 || row_stride < vocab) return fail(ERB_ERR_ARG, "sample_rows: bad vocab/stride");
   if (temperature && !rng_state) return fail(ERB_ERR_ARG, "sample_rows: temperature without rng_state");
-  sample_rows_kernel<<<n_rows, kThreads, 0, (cudaStream_t)stream>>>(logits, row_stride, vocab, temperature,
+  launch_chained(sample_rows_kernel, dim3(n_rows), dim3(kThreads), 0, (cudaStream_t)stream, logits, row_stride, vocab, temperature,
                                                                   rng_state, tokens);
   return check_launch("sample_rows");
 }

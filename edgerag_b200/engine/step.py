@@ -92,7 +92,6 @@ class StepContext:
         self.embeds: torch.Tensor | None = None
         self.max_pages = 1
         self.graph_key: tuple | None = None          # set when the step has the fixed layout of a CUDA graph
-        self.fixed_decode_splits: int | None = None
         self.slots: list[torch.Tensor] = []
         self.block_tables: list[torch.Tensor] = []
         #: host copies for parts that size launches or loop over sequences
@@ -113,10 +112,15 @@ class StepContext:
         """The state tensor ``[slots, ...]`` a mixer registered under ``name`` for a cache layer."""
         return self._runner.pools.states[f"{name}@{cache_layer}"]
 
+    def max_keys_bound(self) -> int:
+        """A power-of-two bound (in pages) on the longest context of the batch, times the page size."""
+        return max(4, 1 << (self.max_pages - 1).bit_length()) * self.page_size
+
     def decode_splits(self, window: int, split_keys: int = kernels.DECODE_SPLIT_KEYS) -> int:
         """Largest number of key splits any single-token sequence of the batch has."""
-        if self.fixed_decode_splits is not None:   # a captured layout: the bound must hold for every replay
-            return self.fixed_decode_splits if window <= 0 else min(self.fixed_decode_splits, window // split_keys + 2)
+        if self.graph_key is not None:   # a captured layout: the bound must hold for every replay
+            bound = -(-(self.max_pages * self.page_size) // split_keys)
+            return bound if window <= 0 else min(bound, window // split_keys + 2)
         most = 1
         for pos in self.host_positions_last[: self.n_decode]:
             lo = max(0, pos - window + 1) if window > 0 else 0
@@ -263,8 +267,8 @@ class ModelRunner:
                 n_embed_rows += n
             for g, row in enumerate(self.cache.slots_for(e.request_id, n)):
                 slots[g, sl] = row
-                pages = rc.tables[g].pages
-                tables[g, s, : len(pages)] = [p if p >= 0 else 0 for p in pages]
+                pages = rc.tables[g].array()
+                tables[g, s, : pages.size] = np.maximum(pages, 0)     # released pages are never read: any id does
             token_of_seq[s] = t0
             seq_starts[s + 1] = t0 + n
             state_slots[s] = rc.slot
@@ -292,7 +296,6 @@ class ModelRunner:
         ctx.max_pages = max_pages
         if graphable:
             ctx.graph_key = (n_seqs, max_pages, int(want_rows.size))
-            ctx.fixed_decode_splits = -(-(max_pages * ps) // kernels.DECODE_SPLIT_KEYS)
         if embed_chunks:
             ctx.embeds = torch.cat([c.to(device=self.device, dtype=self.dtype, non_blocking=True)
                                     for c in embed_chunks], dim=0).contiguous()
@@ -329,8 +332,8 @@ class ModelRunner:
             self.status.zero_()
             self._status_host.zero_()
             if code >= 1000000:
-                raise StepError(f"the tensor-core attention kernel gave up waiting (block {code - 1000000}); "
-                                "the step's results are not valid")
+                raise StepError(f"an attention kernel gave up (code {code}: 1xxxxxx prefill wait, 2xxxxxx decode "
+                                "wait, 3000000 shared-memory alignment); the step's results are not valid")
             raise StepError(f"a kernel flagged token {code - 1} of the batch (id or row out of range)")
 
     def drop_graphs(self) -> None:

@@ -53,7 +53,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
 _LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 2, "erb_linear": 0}
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 16
 
 
 def _fn(library: str, elem: str | None, name: str):
@@ -92,7 +92,8 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The raw handle of the current CUDA stream (the capturing stream inside a graph capture)."""
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def _need(t: torch.Tensor | None, name: str, dtype=None, contiguous: bool = True) -> None:
@@ -208,6 +209,30 @@ def _workspace(device: torch.device) -> torch.Tensor:
     return ws
 
 
+def linear_few_rows_supported(a: torch.Tensor, weight: torch.Tensor, lda: int) -> bool:
+    """Whether the weight-streaming kernel takes these operands (bfloat16, at most 64 rows, 16-byte rows)."""
+    k = a.shape[1]
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= 64 and k % 8 == 0 and lda % 8 == 0
+            and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear_few_rows(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``linear`` through the weight-streaming kernel, for up to 64 rows (``linear`` itself switches to the
+    library above ``SKINNY_MAX_ROWS``, where the library is faster)."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
+    _need(out, "out", contiguous=False)
+    m, k = a.shape
+    n = weight.shape[0]
+    lda = a.stride(0) if m > 1 else max(k, a.stride(0))
+    ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
+    if weight.shape[1] != k or out.shape != (m, n) or a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("linear_few_rows: shapes or strides disagree")
+    if out.dtype not in (torch.bfloat16, torch.float32) or not linear_few_rows_supported(a, weight, lda):
+        raise KernelError("linear_few_rows: operands not supported")
+    _call(_fn("gemm", "bfloat16", "erb_linear_skinny"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+          lda, k, ldo, int(out.dtype == torch.float32), _stream())
+
+
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out[M, N] (+)= a[M, K] @ weight[N, K]^T (library product, float accumulation, no TF32).
 
@@ -225,8 +250,7 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate:
         return
     lda = a.stride(0) if m > 1 else max(k, a.stride(0))
     ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
-    if (m <= SKINNY_MAX_ROWS and a.dtype == torch.bfloat16 and not accumulate and k % 8 == 0 and lda % 8 == 0
-            and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+    if m <= SKINNY_MAX_ROWS and not accumulate and linear_few_rows_supported(a, weight, lda):
         # a handful of rows: this package's weight-streaming kernel instead of the library product
         _call(_fn("gemm", "bfloat16", "erb_linear_skinny"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
               lda, k, ldo, int(out.dtype == torch.float32), _stream())
@@ -260,6 +284,19 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_of_token.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), n, n_q_heads, nkv, d, page_size, int(window),
           float(scale), _stream())
+
+
+def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int) -> int:
+    """Keys per split for the decode kernels: the largest of 512 / 256 / 128 that still gives the GPU
+    a few blocks per SM.  A function of the batch's size and of a power-of-two bound on its longest
+    context only, so an eager step and a captured one make the same choice."""
+    groups = max(1, n_kv_heads // 4)
+    for split in (512, 256, 128):
+        if split % page_size and page_size % split:
+            continue
+        if n_seqs * groups * -(-max_keys // split) >= 4 * 148 or split == 128:
+            return split
+    return DECODE_SPLIT_KEYS
 
 
 def decode_scratch_floats(n_seqs: int, n_q_heads: int, head_dim: int, max_splits: int) -> tuple[int, int]:

@@ -73,17 +73,19 @@ class Attention(Mixer):
         tables = ctx.block_tables[group]
         nd = ctx.n_decode
         if nd:
-            max_splits = ctx.decode_splits(self.window)
+            split = kernels.choose_decode_split(nd, self.n_kv, ctx.max_keys_bound(), ctx.page_size)
+            max_splits = ctx.decode_splits(self.window, split)
             need_acc, need_ml = kernels.decode_scratch_floats(nd, self.n_q, d, max_splits)
             part_acc = ctx.buf("attn.part_acc", (need_acc,), torch.float32)
             part_ml = ctx.buf("attn.part_ml", (need_ml,), torch.float32)
             if kernels.decode_bulk_supported(self.dtype, d, self.window, self.n_q, self.n_kv, max_splits):
                 kernels.attention_decode_bulk(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
-                                              out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status)
+                                              out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,
+                                              split_keys=split)
             else:
                 kernels.attention_decode(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                          out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits,
-                                         window=self.window)
+                                         window=self.window, split_keys=split)
         if n > nd and kernels.prefill_tc_supported(self.dtype, d, self.window):
             n_tiles = sum(-(-q // 128) for q in ctx.host_q_len[nd:])
             kernels.attention_prefill_tc(qkv, k_pages, v_pages, tables[nd:], ctx.seq_starts[nd:], ctx.positions, out,

@@ -69,10 +69,10 @@ def test_growth_then_advance_and_slots():
     rc = m.admit("x")
     assert m.pages_to_grow("x", 17) == [3]
     m.grow("x", 17)
-    assert m.slots_for("x", 3) == [[rc.tables[0].pages[0] * 8 + i for i in range(3)]]
+    assert [r.tolist() for r in m.slots_for("x", 3)] == [[rc.tables[0].pages[0] * 8 + i for i in range(3)]]
     m.advance("x", 17)
     assert rc.num_tokens == 17 and m.pages_to_grow("x", 7) == [0] and m.pages_to_grow("x", 8) == [1]
-    assert m.slots_for("x", 1) == [[rc.tables[0].pages[2] * 8 + 1]]
+    assert [r.tolist() for r in m.slots_for("x", 1)] == [[rc.tables[0].pages[2] * 8 + 1]]
     with pytest.raises(AllocatorError):
         m.advance("x", 9)                      # advancing past the pages: grow first
     m.admit("y")

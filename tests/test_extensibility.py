@@ -147,3 +147,72 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     runner.admit("z")
     again = runner.step([StepEntry("z", tokens=seqs["x"], want=[22])]).cpu()
     torch.testing.assert_close(again[0], want["x"][22], atol=2e-4, rtol=2e-4)
+
+
+def test_windowed_attention_layers_release_pages_behind_the_window(tmp_path):
+    """An architecture registered here whose layers alternate full and windowed attention: two cache
+    groups with pages of their own; the windowed group gives pages back while the request runs (they are
+    poisoned with NaN when freed), and the logits still equal a plain windowed computation."""
+    from edgerag_b200 import Engine
+    from edgerag_b200.config import register_architecture
+    from edgerag_b200.config.registry import architecture_of
+    from edgerag_b200.engine.step import StepEntry
+    from edgerag_b200.models.decoder import DecoderModel
+    from edgerag_b200.parts.base import LayerCall, LayerSpec, ModelPlan, PartSpec
+    from edgerag_b200.weights.loader import write_model_folder
+    import plain_llama as plain
+
+    window, h, nq, nkv, d, inter, vocab, layers = 21, 40, 4, 2, 16, 56, 61, 4
+
+    def make_plan(raw):
+        norm = lambda p: PartSpec("rmsnorm", {"size": h, "eps": 1e-5}, p)   # noqa: E731
+        specs = []
+        for i in range(layers):
+            mixer = PartSpec("attention", {"hidden": h, "n_q_heads": nq, "n_kv_heads": nkv, "head_dim": d,
+                                           "window": window if i % 2 else 0,
+                                           "position": PartSpec("rope_halves", {"head_dim": d, "theta": 500.0})}, "self_attn.")
+            specs.append(LayerSpec(f"layers.{i}.", PartSpec("prenorm"), norm("ln1."), mixer, norm("ln2."),
+                                   PartSpec("swiglu", {"hidden": h, "intermediate": inter}, "mlp.")))
+        return ModelPlan(h, vocab, PartSpec("table", {"vocab": vocab, "hidden": h}, "embed_tokens."), specs,
+                         [LayerCall(i, i) for i in range(layers)], norm("norm."),
+                         PartSpec("linear", {"vocab": vocab, "hidden": h, "tied": False}, "lm_head."))
+
+    register_architecture("ToyWindowForCausalLM", lambda raw, where: raw, make_plan)
+    raw = {"architectures": ["ToyWindowForCausalLM"]}
+    arch = architecture_of(raw)
+    specs = DecoderModel(arch.make_plan(raw), torch.float32, torch.device("cpu")).weight_specs()
+    folder = write_model_folder(tmp_path / "win", raw, specs, seed=5, std=0.2, norm_jitter=0.1, dtype=torch.float32)
+    engine = Engine.from_pretrained(folder, dtype="float32", block_size=4, num_blocks=30, max_batch_size=2,
+                                    poison_freed_pages=True)
+    layout = engine.model.cache_layout
+    assert [(g.n_layers, g.window) for g in layout.groups] == [(2, 0), (2, window)]
+    assert layout.placement == [(0, 0), (1, 0), (0, 1), (1, 1)]
+
+    w = plain.read_weights(folder)
+    seq = torch.randint(0, vocab, (90,), generator=torch.Generator().manual_seed(3)).tolist()
+    cfg = {"head_dim": d, "n_q": nq, "n_kv": nkv, "theta": 500.0}
+    x = w["model.embed_tokens.weight"][torch.tensor(seq)]
+    for i in range(layers):
+        p = f"model.layers.{i}."
+        a = p + "self_attn."
+        x = x + plain.attention(plain.rms_norm(x, w[p + "ln1.weight"], 1e-5), torch.arange(len(seq)), w[a + "q_proj.weight"],
+                                w[a + "k_proj.weight"], w[a + "v_proj.weight"], w[a + "o_proj.weight"], cfg,
+                                window=window if i % 2 else None)
+        m = p + "mlp."
+        x = x + plain.swiglu(plain.rms_norm(x, w[p + "ln2.weight"], 1e-5), w[m + "gate_proj.weight"],
+                             w[m + "up_proj.weight"], w[m + "down_proj.weight"])
+    want = plain.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["lm_head.weight"].T
+
+    runner = engine.runner
+    runner.admit("w")
+    got, fed = [], 0
+    for n in (30, 7, 1, 1, 1, 19, 1, 1, 2, 27):          # portions longer than the window, and single tokens
+        got.append(runner.step([StepEntry("w", tokens=seq[fed: fed + n], want=list(range(n)))]).cpu().clone())
+        fed += n
+        engine.cache.check_invariants()
+    assert fed == len(seq)
+    torch.testing.assert_close(torch.cat(got), want, atol=2e-4, rtol=2e-4)
+    held = engine.cache.held_pages("w")
+    assert held[0] == 23 and held[1] <= (window + 3) // 4 + 1      # the windowed group kept only what is visible
+    runner.release("w")
+    assert engine.cache.free_pages() == [30, 30]

