@@ -135,6 +135,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {          // 2^x, one instruction; -inf gives 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
@@ -201,6 +206,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
 
   // Each thread copies chunk (tid % 8) of rows (tid / 8) + 32 i, so a warp covers whole 128-byte rows.
   const int lc = tid & 7, lr = tid >> 3;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
   auto load_kv = [&](int j) {               // always commits a group, empty past the last tile
     if (j < n_kv) {
       const int stage = j % kKvStages;
@@ -212,8 +218,9 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
         const bool valid = key <= last_key;
         size_t off = 0;
         if (valid) {
-          const int page = bt[key / page_size];
-          off = (((size_t)page * nkv + kvh) * page_size + (key % page_size)) * HD + lc * 8;
+          const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+          const int po = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+          off = (((size_t)bt[pi] * nkv + kvh) * page_size + po) * HD + lc * 8;
         }
         cp_async16(dK + swz(r, lc), k_pages + off, valid);
         cp_async16(dV + swz(r, lc), v_pages + off, valid);
@@ -275,14 +282,15 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     float m_half = -INFINITY;
     if (key0 + 31 <= my_pos) {              // every key of this half is visible to this row
 #pragma unroll
-      for (int i = 0; i < 32; ++i) { s[i] *= scale_log2; m_half = fmaxf(m_half, s[i]); }
+      for (int i = 0; i < 32; ++i) m_half = fmaxf(m_half, s[i]);
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        s[i] = (key0 + i <= my_pos) ? s[i] * scale_log2 : -INFINITY;
+        if (key0 + i > my_pos) s[i] = -INFINITY;
         m_half = fmaxf(m_half, s[i]);
       }
     }
+    m_half *= scale_log2;                   // scale > 0: the maximum of the scaled scores
     // The two threads of a row exchange their maxima through the P buffer of this tile, which is free
     // (P V of tile j-2 was waited for above): each writes into the first bytes of its partner's part of
     // the row and reads its own part, which nobody else touches until the thread overwrites it with P.
@@ -294,7 +302,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     float alpha = 1.f;
     const bool jump = m_tile > m_ref + 8.f;               // true on the first tile (m_ref = -inf)
     if (jump) {
-      alpha = exp2f(m_ref - m_tile);                      // 0 on the first tile
+      alpha = fast_exp2(m_ref - m_tile);                  // 0 on the first tile
       m_ref = m_tile;
     }
     if (j > 0 && __any_sync(0xffffffffu, jump)) {
@@ -317,7 +325,8 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
       uint32_t packed[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float p0 = exp2f(s[8 * g + 2 * i] - m_ref), p1 = exp2f(s[8 * g + 2 * i + 1] - m_ref);
+        const float p0 = fast_exp2(fmaf(s[8 * g + 2 * i], scale_log2, -m_ref));
+        const float p1 = fast_exp2(fmaf(s[8 * g + 2 * i + 1], scale_log2, -m_ref));
         l_tile += p0 + p1;
         __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
         packed[i] = *reinterpret_cast<uint32_t*>(&b);
