@@ -134,8 +134,9 @@ ERB_EXPORT int erb_linear(const void* a, const void* w, void* out, int M, int N,
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-constexpr int kSkWarps = 8;
-constexpr int kSkUnroll = 4;     // passes in flight per warp
+// Warps per block: 8, or 16 when the product has so few rows of w that 8-warp blocks would leave the
+// SMs short of loads in flight (N / 16 blocks is all the parallelism over N there is).
+constexpr int kSkUnroll = 4;     // passes in flight per warp (8 was faster alone and slower inside the step)
 
 __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -145,7 +146,7 @@ __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int NT, bool OUT_F32>   // NT: tiles of 8 rows of `a`
+template <int NT, bool OUT_F32, int kSkWarps>   // NT: tiles of 8 rows of `a`
 __global__ void __launch_bounds__(kSkWarps * 32)
 linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                      int M, int N, int K, int lda, int ldw, int ldo) {
@@ -219,12 +220,16 @@ template <int NT>
 int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw, int ldo,
                   int out_f32, cudaStream_t s) {
   const unsigned blocks = (unsigned)((N + 15) / 16);
-  if (out_f32)
-    launch_chained(linear_skinny_kernel<NT, true>, dim3(blocks), dim3(kSkWarps * 32), 0, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
-                                                                     out, M, N, K, lda, ldw, ldo);
-  else
-    launch_chained(linear_skinny_kernel<NT, false>, dim3(blocks), dim3(kSkWarps * 32), 0, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
-                                                                      out, M, N, K, lda, ldw, ldo);
+  const __nv_bfloat16 *ap = (const __nv_bfloat16*)a, *wp = (const __nv_bfloat16*)w;
+  if constexpr (NT <= 2) {
+    if (blocks < 2 * 148 && K >= 1024) {        // few blocks: twice the warps per block
+      if (out_f32) launch_chained(linear_skinny_kernel<NT, true, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+      else launch_chained(linear_skinny_kernel<NT, false, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+      return check_launch("linear_skinny");
+    }
+  }
+  if (out_f32) launch_chained(linear_skinny_kernel<NT, true, 8>, dim3(blocks), dim3(256), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+  else launch_chained(linear_skinny_kernel<NT, false, 8>, dim3(blocks), dim3(256), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
   return check_launch("linear_skinny");
 }
 
