@@ -337,6 +337,7 @@ def run_serving_workload(args) -> dict:
                    "pool_pages": engine.cache.pages[0].capacity, "page_tokens": 16,
                    "embeds_requests": sum(e is not None for e in embeds)},
         "scheduler": stats, "clocks": clocks.record(),
+        "graphs": {"captured": len(engine.runner._graphs), "replays": engine.runner.graph_replays},
     }
 
 

@@ -152,8 +152,10 @@ class ModelRunner:
         self._meta_turn = 0
         self.steps_run = 0
         self.h2d_bytes_last = 0
-        #: decode-only steps are captured in CUDA graphs, one per (sequences, page bucket, wanted rows)
-        self.graphs_enabled = bool(cuda_graphs)
+        #: steps are captured in CUDA graphs, one per (single tokens, portion lengths, page bucket, wanted
+        #: rows), the second time a layout is seen; only models whose parts all declare ``graph_safe``
+        self.graphs_enabled = bool(cuda_graphs) and bool(getattr(model, "graph_safe", False))
+        self.max_graphs = 512
         self._graphs: dict[tuple, tuple] = {}
         self._graph_seen: dict[tuple, int] = {}
         self.graph_replays = 0
@@ -242,7 +244,9 @@ class ModelRunner:
         for e in ordered:
             rc = self.cache.requests[e.request_id]
             max_pages = max(max_pages, max((len(t.pages) for t in rc.tables), default=1))
-        graphable = self.graphs_enabled and n_decode == n_seqs and all(e.embeds is None for e in ordered)
+        # A step whose layout is fully described by a small key can be replayed from a CUDA graph:
+        # single tokens, and portions of prompts given as ids (their lengths are part of the key).
+        graphable = self.graphs_enabled and all(e.embeds is None for e in ordered)
         if graphable:
             # a captured step has a fixed layout: block tables padded to a power of two of pages
             max_pages = max(4, 1 << (max_pages - 1).bit_length())
@@ -295,7 +299,7 @@ class ModelRunner:
         ctx.n_tokens, ctx.n_seqs, ctx.n_decode, ctx.n_wanted = total, n_seqs, n_decode, int(want_rows.size)
         ctx.max_pages = max_pages
         if graphable:
-            ctx.graph_key = (n_seqs, max_pages, int(want_rows.size))
+            ctx.graph_key = (n_decode, tuple(e.n_tokens for e in ordered[n_decode:]), max_pages, int(want_rows.size))
         if embed_chunks:
             ctx.embeds = torch.cat([c.to(device=self.device, dtype=self.dtype, non_blocking=True)
                                     for c in embed_chunks], dim=0).contiguous()
@@ -358,9 +362,11 @@ class ModelRunner:
             kernels.launch_counts["own"] += hit[2]
             return hit[1]
         seen = self._graph_seen.get(key, 0)
+        if len(self._graph_seen) > 8192:
+            self._graph_seen.clear()
         self._graph_seen[key] = seen + 1
         logits = self.model.forward(ctx)
-        if seen >= 1:
+        if seen >= 1 and len(self._graphs) < self.max_graphs:
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_counts["own"]
             with torch.cuda.graph(graph):

@@ -45,6 +45,9 @@ class DecoderModel:
         self._owners.append((plan.head.prefix, self.head))
         self.schedule: list[LayerCall] = list(plan.schedule)
         self.cache_layout = self._derive_cache_layout()
+        #: every part may be captured in a CUDA graph (an attention mixer also vouches for its position encoding)
+        self.graph_safe = all(part.graph_safe for _, part in self._owners) and all(
+            getattr(getattr(b.mixer, "position", None), "graph_safe", True) for b in self.blocks)
         self.logits_stride = -(-plan.vocab_size // 8) * 8  # rows of the logits buffer start 32-byte aligned
 
     # --- cache needs ------------------------------------------------------------------------------

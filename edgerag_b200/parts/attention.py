@@ -23,6 +23,8 @@ from .base import LayerCall, Mixer, PartSpec, WeightSpec, build_part, register_p
 
 @register_part("mixer", "attention")
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden: int, n_q_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec,
                  dtype: torch.dtype, device: torch.device, window: int = 0, own_kv: bool = True,
                  scale: float | None = None) -> None:

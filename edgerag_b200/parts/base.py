@@ -97,6 +97,12 @@ class ModelPlan:
 class Part:
     """Base of every part: owns tensors, knows their names, holds no reference to a model."""
 
+    #: Whether ``forward`` may be captured in a CUDA graph and replayed for later steps of the same
+    #: layout: everything that changes from step to step must then be read on the device from the
+    #: step context's tensors (never baked in from its host copies), and nothing may allocate or
+    #: synchronise.  Parts that do not say so keep their model on the eager path.
+    graph_safe = False
+
     def weight_specs(self) -> list[WeightSpec]:
         return []
 

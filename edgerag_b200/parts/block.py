@@ -15,6 +15,8 @@ from .base import Block, FeedForward, LayerCall, Mixer, Norm, register_part
 
 @register_part("block", "prenorm")
 class PreNormBlock(Block):
+    graph_safe = True
+
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward, hidden: int,
                  dtype: torch.dtype, device: torch.device) -> None:
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn

@@ -17,6 +17,8 @@ from .base import Part, WeightSpec, register_part
 
 @register_part("embedding", "table")
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab: int, hidden: int, dtype: torch.dtype, device: torch.device) -> None:
         self.vocab, self.hidden = vocab, hidden
         self.dtype, self.device = dtype, device
@@ -35,6 +37,8 @@ class TokenEmbedding(Part):
 
 @register_part("head", "linear")
 class LMHead(Part):
+    graph_safe = True
+
     def __init__(self, vocab: int, hidden: int, tied: bool, dtype: torch.dtype, device: torch.device) -> None:
         self.vocab, self.hidden, self.tied = vocab, hidden, tied
         self.dtype, self.device = dtype, device

@@ -16,6 +16,8 @@ from .base import Norm, WeightSpec, register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device) -> None:
         self.size = size
         self.eps = float(eps)

@@ -20,6 +20,8 @@ from .base import PositionEncoding, register_part
 
 @register_part("position", "rope_halves")
 class RotaryHalves(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim: int, theta: float, dtype: torch.dtype, device: torch.device,
                  rot_dim: int | None = None) -> None:
         self.head_dim = head_dim
@@ -39,6 +41,8 @@ class RotaryHalves(PositionEncoding):
 
 @register_part("position", "none")
 class NoPosition(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, dtype: torch.dtype, device: torch.device, **_unused) -> None:
         pass
 

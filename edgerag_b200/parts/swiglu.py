@@ -13,6 +13,8 @@ from .base import FeedForward, WeightSpec, register_part
 
 @register_part("ffn", "swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden: int, intermediate: int, dtype: torch.dtype, device: torch.device) -> None:
         self.hidden, self.intermediate = hidden, intermediate
         self.dtype, self.device = dtype, device

@@ -82,6 +82,24 @@ def test_cuda_graph_decode_equals_eager_decode(model_folders):
         rows[graphs] = torch.stack(got)
         assert (r.graph_replays > 0) == graphs
     assert torch.equal(rows[True], rows[False])
+    # steps that mix a portion of a prompt with single tokens are captured too, once their layout repeats
+    rows = {}
+    for graphs in (False, True):
+        engine = Engine.from_pretrained(folder, dtype="bfloat16", block_size=8, num_blocks=200, max_batch_size=8,
+                                        cuda_graphs=graphs)
+        r = engine.runner
+        r.admit("x"), r.admit("y")
+        r.step([StepEntry("x", tokens=prompts[0]), StepEntry("y", tokens=prompts[1])])
+        got = []
+        for i in range(10):           # the same layout again and again: a 16-token portion of a new request beside two single tokens
+            r.admit(f"p{i}")
+            out = r.step([StepEntry(f"p{i}", tokens=prompts[2][:16], want=[3, 15]), StepEntry("x", tokens=[i + 1], want=[0]),
+                          StepEntry("y", tokens=[i + 2], want=[0])])
+            got.append(out.clone())
+            r.release(f"p{i}")
+        rows[graphs] = torch.stack(got)
+        assert (r.graph_replays >= 4) == graphs
+    assert torch.equal(rows[True], rows[False])
 
 
 def test_prompt_embeds_temperature_and_eos(model_folders):
