@@ -174,3 +174,26 @@ def test_command_line(model_folders, tmp_path):
     assert proc.returncode == 0, proc.stderr[-3000:]
     assert (tmp_path / "rw" / "model.safetensors").is_file()
     assert len(json.loads(proc.stdout.strip().splitlines()[-1])["outputs"][0]["token_ids"]) == 4
+
+
+def test_many_requests_through_a_small_pool_equal_each_alone(model_folders):
+    """Continuous batching under pressure: a dozen requests of assorted lengths, a pool that holds
+    about three of them, short portions, several prompts per step.  Every request must produce the
+    tokens it produces alone (edgerag tests/test_executor.py:164-191), and every page must come back."""
+    from edgerag_b200 import Engine, SamplingParams
+
+    folder = model_folders("b", "float32", std=0.2)
+    cfg = plain.read_config(folder)
+    lens = [5, 61, 17, 40, 9, 77, 23, 3, 50, 31, 12, 66]
+    news = [9, 4, 17, 6, 30, 5, 12, 25, 7, 11, 19, 3]
+    prompts = [helpers.random_sequence(cfg["vocab"], n, 300 + n) for n in lens]
+    solo = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=64, chunk_size=512, max_batch_size=1)
+    want = [solo.generate([p], SamplingParams(max_new_tokens=n))[0] for p, n in zip(prompts, news)]
+    busy = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=30, chunk_size=11, max_batch_size=5,
+                                  max_prefills_per_step=2, poison_freed_pages=True)
+    got = busy.generate(prompts, [SamplingParams(max_new_tokens=n) for n in news])
+    assert got == want
+    stats = busy.scheduler.stats
+    assert stats.finished == len(prompts) and stats.admission_blocked > 0 and stats.preempted == 0
+    assert busy.cache.free_pages() == [30] and busy.cache.slots.num_free == 5
+    busy.cache.check_invariants()
