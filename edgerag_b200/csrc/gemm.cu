@@ -147,16 +147,36 @@ __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t 
 }
 
 template <int NT, bool OUT_F32, int kSkWarps>   // NT: tiles of 8 rows of `a`
-__global__ void __launch_bounds__(kSkWarps * 32)
+__global__ void __launch_bounds__(kSkWarps * 32, NT == 1 ? 32 / kSkWarps : 1)
 linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                      int M, int N, int K, int lda, int ldw, int ldo) {
-  chain_wait();
   __shared__ float red[kSkWarps][NT][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
   const int n0 = blockIdx.x * 16;
   const uint4* w_lo = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + r, N - 1) * ldw);
   const uint4* w_hi = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + r + 8, N - 1) * ldw);
+  const int chunks = K >> 3;                          // 16-byte chunks per row
+  const int passes = (chunks + 3) >> 2;               // 4 chunks (32 k) per pass
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  constexpr int kStride = kSkWarps * kSkUnroll;
+
+  // The weights are constants, so the first round of fragments does not depend on the kernel before
+  // this one and is loaded before chain_wait(), while that kernel (a norm, an activation, the combine
+  // of attention) may still be running.
+  uint4 lo[kSkUnroll], hi[kSkUnroll];
+  auto load_w = [&](int p0) {
+#pragma unroll
+    for (int u = 0; u < kSkUnroll; ++u) {
+      const int c = (p0 + u * kSkWarps) * 4 + j;
+      const bool in = c < chunks;
+      lo[u] = in ? __ldcs(w_lo + c) : zero;
+      hi[u] = in ? __ldcs(w_hi + c) : zero;
+    }
+  };
+  load_w(warp);
+  chain_wait();
+
   const uint4* a_row[NT];
   bool a_ok[NT];
 #pragma unroll
@@ -170,18 +190,7 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
 
-  const int chunks = K >> 3;                          // 16-byte chunks per row
-  const int passes = (chunks + 3) >> 2;               // 4 chunks (32 k) per pass
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int p0 = warp; p0 < passes; p0 += kSkWarps * kSkUnroll) {
-    uint4 lo[kSkUnroll], hi[kSkUnroll];
-#pragma unroll
-    for (int u = 0; u < kSkUnroll; ++u) {
-      const int c = (p0 + u * kSkWarps) * 4 + j;
-      const bool in = c < chunks;
-      lo[u] = in ? __ldcs(w_lo + c) : zero;
-      hi[u] = in ? __ldcs(w_hi + c) : zero;
-    }
+  auto multiply = [&](int p0) {
 #pragma unroll
     for (int u = 0; u < kSkUnroll; ++u) {
       const int c = (p0 + u * kSkWarps) * 4 + j;
@@ -195,6 +204,11 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
         mma_16816(acc[t], a1, x.z, x.w);
       }
     }
+  };
+  if (warp < passes) multiply(warp);
+  for (int p0 = warp + kStride; p0 < passes; p0 += kStride) {
+    load_w(p0);
+    multiply(p0);
   }
 #pragma unroll
   for (int t = 0; t < NT; ++t)
