@@ -47,6 +47,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--eos-token-id", type=int, default=None)
+    ap.add_argument("--no-lookahead", action="store_true",
+                    help="read every step's tokens before the next step is launched")
+    ap.add_argument("--no-cuda-graphs", action="store_true", help="launch every kernel of every step from the host")
     ap.add_argument("--prompt-ids", action="append", default=[], metavar="IDS",
                     help="a prompt as token ids, comma or space separated; may be given several times")
     ap.add_argument("--prompt-file", help="a file with one prompt per line (token ids)")
@@ -73,7 +76,8 @@ def main(argv: list[str] | None = None) -> int:
         dtype=args.dtype, device=args.device, block_size=args.block_size, num_blocks=args.num_blocks,
         budget_gib=args.budget_gib or None, kv_fraction=args.kv_fraction, max_batch_size=args.max_batch_size,
         chunk_size=args.chunk_size, max_prefills_per_step=args.max_prefills_per_step,
-        max_model_len=args.max_model_len, eos_token_id=args.eos_token_id, seed=args.seed)
+        max_model_len=args.max_model_len, eos_token_id=args.eos_token_id, seed=args.seed,
+        lookahead=not args.no_lookahead, cuda_graphs=not args.no_cuda_graphs)
     t0 = time.perf_counter()
     if args.model is not None:
         engine = Engine.from_pretrained(args.model, options)

@@ -413,3 +413,23 @@ ERB_EXPORT int erb_gather_cast(const float* src, void* dst, const int* rows, int
   launch_chained(gather_cast_kernel<elem_t>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, src, (elem_t*)dst, rows, width);
   return check_launch("gather_cast");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Token ids that are still on the device: an id t < 0 in `ids` stands for row -t - 1 of `fed`, the
+// tokens the sampler wrote for the step before (the host launches the next step before it has read
+// them).  A row outside `fed` leaves the id negative, which the embedding kernel then flags.
+// ---------------------------------------------------------------------------------------------
+__global__ void resolve_ids_kernel(int* __restrict__ ids, int n, const int* __restrict__ fed, int n_fed) {
+  chain_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const int id = ids[t];
+  if (id < 0 && -id - 1 < n_fed) ids[t] = fed[-id - 1];
+}
+
+ERB_EXPORT int erb_resolve_ids(int* ids, int n, const int* fed, int n_fed, void* stream) {
+  if (n <= 0) return ERB_OK;
+  if (!ids || !fed || n_fed <= 0) return fail(ERB_ERR_ARG, "resolve_ids: no buffer of fed-back tokens");
+  launch_chained(resolve_ids_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, (cudaStream_t)stream, ids, n, fed, n_fed);
+  return check_launch("resolve_ids");
+}

@@ -134,7 +134,7 @@ ERB_EXPORT int erb_linear(const void* a, const void* w, void* out, int M, int N,
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-// Warps per block: 8, or 16 when the product has so few rows of w that 8-warp blocks would leave the
+// Warps per block: 8; 16 (or 32, for rows of 4096 k and more) when the product has so few rows of w that 8-warp blocks would leave the
 // SMs short of loads in flight (N / 16 blocks is all the parallelism over N there is).
 constexpr int kSkUnroll = 4;     // passes in flight per warp (8 was faster alone and slower inside the step)
 
@@ -235,6 +235,13 @@ int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, 
                   int out_f32, cudaStream_t s) {
   const unsigned blocks = (unsigned)((N + 15) / 16);
   const __nv_bfloat16 *ap = (const __nv_bfloat16*)a, *wp = (const __nv_bfloat16*)w;
+  if constexpr (NT == 1) {
+    if (blocks <= 148 && K >= 4096) {           // at most one block per SM and long rows: 32 warps per block
+      if (out_f32) launch_chained(linear_skinny_kernel<NT, true, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+      else launch_chained(linear_skinny_kernel<NT, false, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+      return check_launch("linear_skinny");
+    }
+  }
   if constexpr (NT <= 2) {
     if (blocks < 2 * 148 && K >= 1024) {        // few blocks: twice the warps per block
       if (out_f32) launch_chained(linear_skinny_kernel<NT, true, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);

@@ -26,10 +26,11 @@ from ..cache.manager import CacheManager, OutOfPagesError
 from ..config.registry import architecture_of, read_model_folder
 from ..models.decoder import DecoderModel
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler
+from ..sampling.sampler import PendingTokens, Sampler
 from ..weights.loader import load_safetensors, random_tensors
 from .request import Request, RequestState
-from .scheduler import Batch, Scheduler, SchedulerConfig
+from .scheduler import Batch, ScheduledEntry, Scheduler, SchedulerConfig
+from ..cache.allocator import OutOfPagesError
 from .step import ModelRunner, StepEntry
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -79,6 +80,9 @@ class EngineOptions:
     overcommit: bool = False
     seed: int = 0
     cuda_graphs: bool = True
+    #: launch the next decoding step before this step's tokens have reached the host (they are fed
+    #: back on the device); what ``step`` returns is then one step behind what the GPU is running
+    lookahead: bool = True
     poison_freed_pages: bool = False    # tests: NaN in free pages, so a stale read shows
 
 
@@ -91,6 +95,15 @@ class TokenEvent:
     index: int
     finished: bool
     finish_reason: str | None = None
+
+
+@dataclass
+class _Launched:
+    """A step on the device: its batch, the entries whose last logits are sampled, and the ids on their way."""
+
+    batch: Batch
+    sampled: list[ScheduledEntry]
+    pending: PendingTokens | None
 
 
 class Engine:
@@ -132,6 +145,8 @@ class Engine:
         self.sampler = Sampler(self.device)
         self._next_id = 0
         self._requests: dict[str, Request] = {}
+        self._in_flight: _Launched | None = None   # a step that runs on the device and has not been collected
+        self.lookahead_steps = 0
         self.d2h_bytes_last = 0
 
     # --- construction -------------------------------------------------------------------------------
@@ -204,51 +219,107 @@ class Engine:
 
     @property
     def has_work(self) -> bool:
-        return self.scheduler.has_work
+        return self.scheduler.has_work or self._in_flight is not None
 
     # --- one iteration ------------------------------------------------------------------------------
 
-    def _entries(self, batch: Batch) -> list[StepEntry]:
+    def _entries(self, batch: Batch, fed_rows: dict[str, int] | None = None) -> list[StepEntry]:
         entries = []
         for e in batch.entries:
             r = e.request
             want = [e.n_tokens - 1] if e.samples else []
-            if e.from_embeds:
+            if fed_rows is not None:
+                entries.append(StepEntry(r.request_id, fed_back=fed_rows[r.request_id], want=want))
+            elif e.from_embeds:
                 entries.append(StepEntry(r.request_id, embeds=r.prompt_embeds[e.start: e.start + e.n_tokens], want=want))
             else:
                 entries.append(StepEntry(r.request_id, tokens=[r.token_at(i) for i in range(e.start, e.start + e.n_tokens)],
                                          want=want))
         return entries
 
-    def step(self) -> list[TokenEvent]:
-        """Schedule, run and sample one batch.  Returns the tokens generated in this step."""
-        batch = self.scheduler.schedule()
-        if batch.is_empty:
-            return []
+    def _launch(self, batch: Batch, after: "_Launched | None" = None) -> "_Launched":
+        """Put one batch on the device: the step, the sampling kernel and the copy of the ids to the
+        host.  ``after``: the step before, not yet collected; the batch's tokens are its samples."""
+        fed_rows = None
+        if after is not None:
+            fed_rows = {e.request.request_id: row for row, e in enumerate(after.sampled)}
+            self.runner.feedback = self.sampler.device_tokens
         try:
-            logits = self.runner.step(self._entries(batch))
+            logits = self.runner.step(self._entries(batch, fed_rows))
         except Exception as exc:
+            if after is not None:
+                raise
             # Every request of the batch fails and frees its pages; the engine stays usable
             # (edgerag/serve/engine.py:178-189).
             for e in batch.entries:
                 self.scheduler.abort(e.request, f"error: {type(exc).__name__}")
             raise
         sampled = [e for e in batch.entries if e.samples]
-        new_tokens: dict[str, int] = {}
+        pending = None
         if sampled:
-            tokens = self.sampler.sample(
+            ahead = 0 if after is None else 1            # the token of `after` is not in num_generated yet
+            pending = self.sampler.launch(
                 logits, [e.request.sampling for e in sampled], [e.request.seed for e in sampled],
-                [e.request.num_generated for e in sampled])
-            new_tokens = {e.request.request_id: t for e, t in zip(sampled, tokens)}
-            self.runner.raise_if_flagged()       # the sampler synchronised: the status copy is current
+                [e.request.num_generated + ahead for e in sampled])
+        return _Launched(batch, sampled, pending)
+
+    def _following(self, cur: "_Launched") -> Batch | None:
+        """The batch that follows ``cur`` if nothing unforeseen happens in it, or None when the next
+        decision needs ``cur``'s tokens or the scheduler's judgement: every request of ``cur``
+        samples (so each decodes next), those that reach their length limit with ``cur``'s token
+        drop out, nobody else runs or could be admitted, and the pages for one more token are free."""
+        sched = self.scheduler
+        if not cur.sampled or len(cur.sampled) != len(cur.batch.entries) or len(sched.running) != len(cur.sampled):
+            return None
+        going = [e for e in cur.sampled if e.request.num_generated + 1 < e.request.max_new_tokens
+                 and not e.request.is_finished]
+        if not going or (sched.waiting and len(going) < sched.config.max_batch_size):
+            return None
+        need = [0] * len(self.cache.pages)
+        for e in going:
+            for g, n in enumerate(self.cache.pages_to_grow(e.request.request_id, 1)):
+                need[g] += n
+        if any(n > f for n, f in zip(need, self.cache.free_pages())):
+            return None
+        return Batch(cur.batch.step + 1, [ScheduledEntry(e.request, e.start + e.n_tokens, 1, False, True) for e in going])
+
+    def _collect(self, done: "_Launched") -> list[TokenEvent]:
+        """Read a launched step's tokens and commit it.  Entries of requests that finished meanwhile
+        (a stop token in the step before) are dropped."""
+        live = [e for e in done.sampled if not e.request.is_finished]
+        new_tokens: dict[str, int] = {}
+        if done.pending is not None:
+            tokens = done.pending.read()
+            new_tokens = {e.request.request_id: t for e, t in zip(done.sampled, tokens)}
+            self.runner.raise_if_flagged()       # reading synchronised: the status copy is current
             self.d2h_bytes_last = 4 * len(tokens)
-        self.scheduler.update(batch, new_tokens)
+        self.scheduler.update(done.batch, new_tokens)
         events = []
-        for e in sampled:
+        for e in live:
             r = e.request
             events.append(TokenEvent(r.request_id, new_tokens[r.request_id], r.num_generated - 1,
                                      r.state == RequestState.FINISHED, r.finish_reason))
         return events
+
+    def step(self) -> list[TokenEvent]:
+        """One iteration: returns the tokens of the oldest step that is on the device, after having
+        launched the step that follows it where that needs no decision (``lookahead``).  Without
+        lookahead: schedule, run and sample one batch, and return its tokens."""
+        cur, self._in_flight = self._in_flight, None
+        if cur is None:
+            batch = self.scheduler.schedule()
+            if batch.is_empty:
+                return []
+            cur = self._launch(batch)
+        if self.options.lookahead:
+            follow = self._following(cur)
+            if follow is not None:
+                try:
+                    self._in_flight = self._launch(follow, after=cur)
+                    self.lookahead_steps += 1
+                except OutOfPagesError:
+                    pass        # nothing was changed; the scheduler decides after this step
+        return self._collect(cur)
 
     def generate(self, prompts: list[list[int]] | None = None, sampling: SamplingParams | list[SamplingParams] | None = None,
                  prompt_embeds: list[torch.Tensor | None] | None = None) -> list[list[int]]:
@@ -260,7 +331,7 @@ class Engine:
         for i in range(n):
             emb = prompt_embeds[i] if prompt_embeds is not None else None
             ids.append(self.add_request(prompts[i] if prompts is not None else None, params[i], emb))
-        while self.scheduler.has_work:
+        while self.has_work:
             before = self.scheduler.step_index
             self.step()
             if self.scheduler.step_index == before and not self.scheduler.running:

@@ -246,12 +246,15 @@ class Scheduler:
 
     def update(self, batch: Batch, new_tokens: dict[str, int]) -> list[Request]:
         """Commit a step that ran: advance every entry, append sampled tokens, finish and free.
+        Entries of requests that have finished since the step was launched are skipped.
 
         Returns the requests that finished in this step.
         """
         done = []
         for e in batch.entries:
             r = e.request
+            if r.is_finished:
+                continue        # launched ahead for a request that stopped in the step before: dropped
             r.num_computed += e.n_tokens
             if e.is_decode:
                 self.stats.decode_tokens += 1

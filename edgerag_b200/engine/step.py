@@ -16,6 +16,7 @@ and the row kernel each see a contiguous range; the caller's order is restored i
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -35,15 +36,20 @@ class StepError(ValueError):
 
 @dataclass
 class StepEntry:
-    """The next tokens of one request: ids, or rows of embeddings ``[n, hidden]``; never both."""
+    """The next tokens of one request: ids, or rows of embeddings ``[n, hidden]``, or ``fed_back``:
+    one token that is still on the device, row ``fed_back`` of the runner's ``feedback`` tensor
+    (what the sampler wrote for the step before).  Exactly one of the three."""
 
     request_id: object
     tokens: list[int] | None = None
     embeds: torch.Tensor | None = None
     want: list[int] = field(default_factory=list)
+    fed_back: int | None = None
 
     @property
     def n_tokens(self) -> int:
+        if self.fed_back is not None:
+            return 1
         return len(self.tokens) if self.embeds is None else int(self.embeds.shape[0])
 
 
@@ -86,7 +92,7 @@ class StepContext:
         self.page_size = runner.cache.page_size
         self.dtype = runner.dtype
         self.status = runner.status
-        self.n_tokens = self.n_seqs = self.n_decode = self.n_wanted = 0
+        self.n_tokens = self.n_seqs = self.n_decode = self.n_wanted = self.n_fed_back = 0
         self.token_ids = self.embed_row = self.positions = self.seq_of_token = None
         self.token_of_seq = self.want_rows = self.state_slots = self.seq_starts = None
         self.embeds: torch.Tensor | None = None
@@ -143,6 +149,8 @@ class ModelRunner:
         self.workspace = Workspace(self.device)
         self.workspace.on_move = self.drop_graphs
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        #: int32 device tensor that entries with ``fed_back`` take their token from (set by the caller)
+        self.feedback: torch.Tensor | None = None
         #: host copy of the status word, refreshed asynchronously at the end of every step
         self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self._meta_dev: torch.Tensor | None = None
@@ -198,8 +206,10 @@ class ModelRunner:
             if e.request_id in seen:
                 raise StepError(f"request {e.request_id!r} appears twice in one step")
             seen.add(e.request_id)
-            if (e.tokens is None) == (e.embeds is None):
-                raise StepError(f"request {e.request_id!r}: pass exactly one of tokens or embeds")
+            if (e.tokens is not None) + (e.embeds is not None) + (e.fed_back is not None) != 1:
+                raise StepError(f"request {e.request_id!r}: pass exactly one of tokens, embeds or fed_back")
+            if e.fed_back is not None and (self.feedback is None or not 0 <= e.fed_back < self.feedback.numel()):
+                raise StepError(f"request {e.request_id!r}: no fed-back token in row {e.fed_back}")
             n = e.n_tokens
             if n <= 0:
                 raise StepError(f"request {e.request_id!r}: an entry needs at least one token")
@@ -263,7 +273,9 @@ class ModelRunner:
             sl = slice(t0, t0 + n)
             positions[sl] = np.arange(past, past + n, dtype=np.int32)
             seq_of_token[sl] = s
-            if e.embeds is None:
+            if e.fed_back is not None:
+                token_ids[sl] = -1 - e.fed_back
+            elif e.embeds is None:
                 token_ids[sl] = np.asarray(e.tokens, dtype=np.int32)
             else:
                 embed_row[sl] = np.arange(n_embed_rows, n_embed_rows + n, dtype=np.int32)
@@ -298,6 +310,7 @@ class ModelRunner:
         ctx.block_tables = [tables_d[g * per: (g + 1) * per].view(n_seqs, max_pages) for g in range(n_groups)]
         ctx.n_tokens, ctx.n_seqs, ctx.n_decode, ctx.n_wanted = total, n_seqs, n_decode, int(want_rows.size)
         ctx.max_pages = max_pages
+        ctx.n_fed_back = sum(1 for e in ordered if e.fed_back is not None)
         if graphable:
             ctx.graph_key = (n_decode, tuple(e.n_tokens for e in ordered[n_decode:]), max_pages, int(want_rows.size))
         if embed_chunks:
@@ -319,6 +332,8 @@ class ModelRunner:
         # pages given back since the last step are overwritten before any of them is handed out again
         self.pools.poison_pages(self.cache.drain_freed())
         ctx, ordered = self.prepare(entries)
+        if ctx.n_fed_back:
+            kernels.resolve_ids(ctx.token_ids, self.feedback, self.dtype)
         logits = self._forward(ctx)
         self.finish(ordered)
         self.steps_run += 1
@@ -369,8 +384,17 @@ class ModelRunner:
         if seen >= 1 and len(self._graphs) < self.max_graphs:
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_counts["own"]
-            with torch.cuda.graph(graph):
-                captured = self.model.forward(ctx)
+            # No cyclic garbage collection while the stream captures: a collector run could destroy
+            # tensors or graphs of an engine that is no longer referenced, which is not permitted
+            # during a capture and would invalidate it.
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    captured = self.model.forward(ctx)
+            finally:
+                if collecting:
+                    gc.enable()
             own = kernels.launch_counts["own"] - before
             kernels.launch_counts["own"] = before       # capturing launched nothing
             self._graphs[key] = (graph, captured, own)

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "erb_rope_cache_write": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_swiglu": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "erb_resolve_ids": [c_void_p, c_int, c_void_p, c_int, c_void_p],
     "erb_gather_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "erb_linear": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_void_p, c_longlong, c_void_p],
@@ -150,6 +151,15 @@ def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
         raise KernelError("residual_add: shapes disagree")
     _call(_fn("elementwise", _elem(delta), "erb_residual_add"), hidden.data_ptr(), delta.data_ptr(),
           hidden.numel(), _stream())
+
+
+def resolve_ids(ids: torch.Tensor, fed: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> None:
+    """Replace every id t < 0 of ``ids`` (int32, in place) by ``fed[-t - 1]``: tokens of the step
+    before that are still on the device.  ``dtype`` only picks the library that holds the kernel
+    (the engine's element type, so that nothing else has to be built)."""
+    _need(ids, "ids", torch.int32); _need(fed, "fed", torch.int32)
+    _call(_fn("elementwise", _ELEM[dtype], "erb_resolve_ids"), ids.data_ptr(), ids.numel(),
+          fed.data_ptr(), fed.numel(), _stream())
 
 
 def gather_cast(src: torch.Tensor, dst: torch.Tensor, rows: torch.Tensor | None) -> None:

@@ -5,8 +5,8 @@
     python -m edgerag_b200.ops.microbench linear --m 8 --n 6144 --k 2048
 
 Each case builds random inputs larger than the 126 MB L2 where the real workload is (or says that
-it is not), runs warm-up launches, then times ``--iters`` launches one by one with CUDA events and
-prints one JSON line with the median.  The same commands, under ``ncu``, produce the summaries in
+it is not), runs warm-up launches, then times ``--iters`` launches replayed from one CUDA graph with
+CUDA events and prints one JSON line with the median per launch.  The same commands, under ``ncu``, produce the summaries in
 ``profiles/``.
 """
 
@@ -25,20 +25,28 @@ HBM_GBS, BF16_TFLOPS = 6650.0, 1590.0   # the pool's earlier measurement, used w
 
 
 def _time(fn, iters: int, warmup: int, rounds: int = 5) -> float:
-    """Median over ``rounds`` of the time per launch of ``iters`` launches issued back to back, in
-    microseconds (one launch at a time would time the host's launch path, not the kernel)."""
+    """Median over ``rounds`` of the time per launch of ``iters`` launches, in microseconds.  The launches
+    are captured into one CUDA graph and replayed, so that kernels of a few microseconds are timed
+    back to back as they run inside a step, not at the rate the host can issue them."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    times = []
-    for _ in range(rounds):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b.record()
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(iters):
+                fn()
+        graph.replay()
         torch.cuda.synchronize()
-        times.append(a.elapsed_time(b) * 1e3 / iters)
+        times = []
+        for _ in range(rounds):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / iters)
     return statistics.median(times)
 
 

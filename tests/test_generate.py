@@ -197,3 +197,39 @@ def test_many_requests_through_a_small_pool_equal_each_alone(model_folders):
     assert stats.finished == len(prompts) and stats.admission_blocked > 0 and stats.preempted == 0
     assert busy.cache.free_pages() == [30] and busy.cache.slots.num_free == 5
     busy.cache.check_invariants()
+
+
+def test_lookahead_changes_no_token(model_folders):
+    """With lookahead the engine launches the next decoding step before it has read this step's
+    tokens (they are fed back on the device).  Greedy and seeded temperature requests of assorted
+    lengths, a stop token that ends one request in the middle (so that a step launched ahead has to
+    be dropped for it), a queue that waits for slots: every request produces what it produces
+    without lookahead, the events come in the same order, and every page comes back."""
+    from edgerag_b200 import Engine, SamplingParams
+
+    folder = model_folders("a", "float32", std=0.2)
+    cfg = plain.read_config(folder)
+    prompts = [helpers.random_sequence(cfg["vocab"], n, 500 + n) for n in (12, 33, 5, 21, 40, 9)]
+    params = [SamplingParams(max_new_tokens=n) for n in (20, 7, 31, 1, 12, 26)]
+    params[1] = SamplingParams(max_new_tokens=18, temperature=0.8, seed=3)
+    params[4] = SamplingParams(max_new_tokens=15, temperature=1.3, seed=9)
+    probe = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=64, max_batch_size=1, lookahead=False)
+    eos = probe.generate([prompts[0]], SamplingParams(max_new_tokens=20))[0][9]      # request 0 stops at its tenth token at the latest
+    runs = {}
+    for ahead in (False, True):
+        engine = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=40, chunk_size=16, max_batch_size=4,
+                                        max_prefills_per_step=2, eos_token_id=eos, lookahead=ahead, poison_freed_pages=True)
+        for p, sp in zip(prompts, params):
+            engine.add_request(p, sp)
+        events = []
+        while engine.has_work:
+            events.extend((e.request_id, e.token_id, e.index, e.finished, e.finish_reason) for e in engine.step())
+        runs[ahead] = (events, [engine.request(f"req-{i}").generated_token_ids for i in range(len(prompts))])
+        assert (engine.lookahead_steps > 10) == ahead
+        assert engine.cache.free_pages() == [40] and engine.cache.slots.num_free == 4
+        engine.cache.check_invariants()
+        assert engine.request("req-0").finish_reason == "stop" and len(runs[ahead][1][0]) <= 10
+    assert runs[True][1] == runs[False][1]
+    assert sorted(runs[True][0]) == sorted(runs[False][0])
+    for rid in {e[0] for e in runs[True][0]}:         # each request's events in order, with and without
+        assert [e for e in runs[True][0] if e[0] == rid] == [e for e in runs[False][0] if e[0] == rid]
