@@ -296,17 +296,36 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
           float(scale), _stream())
 
 
+_sm_counts: dict[int, int] = {}
+
+
 def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int) -> int:
-    """Keys per split for the decode kernels: the largest of 512 / 256 / 128 that still gives the GPU
-    a few blocks per SM.  A function of the batch's size and of a power-of-two bound on its longest
-    context only, so an eager step and a captured one make the same choice."""
+    """Keys per split for the decode kernels, from 128 to 2048.
+
+    The bulk kernel runs one block per (sequence, group of four kv heads, split), two blocks per SM.
+    Measured on the decode step (24 layers, contexts of 8,192, batches of 1 to 16): best is the
+    largest split that still fills most of one wave of blocks; a little more than one wave is worst
+    (the few blocks of the second wave stream alone, far below the memory's bandwidth); from about
+    two waves on, the largest such split.  A function of the batch's size and of a power-of-two
+    bound on its longest context only, so an eager step and a captured one make the same choice.
+    """
+    device = torch.cuda.current_device()
+    sms = _sm_counts.get(device)
+    if sms is None:
+        sms = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    slots = 2 * sms
     groups = max(1, n_kv_heads // 4)
-    for split in (512, 256, 128):
-        if split % page_size and page_size % split:
-            continue
-        if n_seqs * groups * -(-max_keys // split) >= 4 * 148 or split == 128:
-            return split
-    return DECODE_SPLIT_KEYS
+    fits = [s for s in (2048, 1024, 512, 256, 128) if s % page_size == 0 or page_size % s == 0]
+    if not fits:
+        return DECODE_SPLIT_KEYS
+    blocks = {s: n_seqs * groups * -(-max_keys // s) for s in fits}
+    for s in fits:                       # most of one wave
+        if 0.6 * slots <= blocks[s] <= slots:
+            return s
+    for s in fits:                       # well beyond one wave
+        if blocks[s] >= 1.7 * slots:
+            return s
+    return fits[-1] if blocks[fits[-1]] < slots else min(fits, key=lambda s: abs(blocks[s] - slots))
 
 
 def decode_scratch_floats(n_seqs: int, n_q_heads: int, head_dim: int, max_splits: int) -> tuple[int, int]:
