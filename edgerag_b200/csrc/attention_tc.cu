@@ -467,7 +467,9 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
                              float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
                              int nkv, int page_size, int split_keys, float scale_log2, int hg,
                              int* __restrict__ status) {
-  chain_wait();
+  // Everything up to chain_wait() below reads only what earlier steps or the host wrote (the batch's
+  // metadata, keys and values of earlier tokens), so it runs while the kernel before this one (the
+  // one that rotates q and writes this step's keys and values) is still at work.
   // hg: kv heads handled by this block.  The rows of hg neighbouring heads of one page are contiguous
   // in the cache, so a block that takes them together copies hg * page_size rows in one piece; with
   // small pages that is what keeps the copies long enough for the memory system.
@@ -542,8 +544,15 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
       }
     }
   };
+  // Tiles that end before the page of the new token hold nothing this step has written.
+  const int old_end = (pos / page_size) * page_size;
+  int issued = 0;
   if (tid == 0) {
-    for (int i = 0; i < kStages && i < n_tiles; ++i) issue(i);
+    while (issued < kStages && issued < n_tiles && min(end, begin + (issued + 1) * STAGE_KEYS) <= old_end) issue(issued++);
+  }
+  chain_wait();
+  if (tid == 0) {
+    for (int i = issued; i < kStages && i < n_tiles; ++i) issue(i);
   }
 
   // This lane's slice of every query head of the group, pre-multiplied by scale * log2(e).

@@ -106,13 +106,17 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __r
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
                                         int write_back) {
-  chain_wait();
   extern __shared__ float row_cache[];
   float* scratch = row_cache + hidden_size;
   const int o = blockIdx.x;
-  const int r = rows ? rows[o] : o;
+  const int r = rows ? rows[o] : o;            // the step's metadata: not written by the kernel before
   float* h = hidden + (size_t)r * hidden_size;
   const T* d = delta ? delta + (size_t)r * hidden_size : nullptr;
+  // the norm's weight is a constant: this thread's first four are loaded before the wait
+  const int i_first = threadIdx.x * 4;
+  float w_first[4] = {0.f, 0.f, 0.f, 0.f};
+  if (i_first < hidden_size) load4(weight + i_first, w_first);
+  chain_wait();
   float ss = 0.f;
   for (int i = threadIdx.x * 4; i < hidden_size; i += blockDim.x * 4) {
     float v[4];
@@ -133,7 +137,12 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __r
   for (int i = threadIdx.x * 4; i < hidden_size; i += blockDim.x * 4) {
     float v[4], w[4];
     load4(row_cache + i, v);
-    load4(weight + i, w);
+    if (i == i_first) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = w_first[j];
+    } else {
+      load4(weight + i, w);
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = w[j] * Elem<T>::round(v[j] * rs);
     Pack4<T>::store(y + i, v);
@@ -147,7 +156,9 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
   const size_t smem = (size_t)(hidden_size + 32) * sizeof(float);
   if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "add_rmsnorm: hidden_size %d too large", hidden_size);
   if (rows && write_back) return fail(ERB_ERR_ARG, "add_rmsnorm: row selection cannot write back");
-  const int threads = hidden_size >= 4096 ? 512 : (hidden_size >= 512 ? 256 : 128);
+  // Threads per row depend on the width only, so a row's sum is formed in the same order whatever the
+  // batch; at 2048 and more, one pass of 16-byte loads per thread (the row's latency is paid once).
+  const int threads = hidden_size >= 2048 ? 512 : (hidden_size >= 512 ? 256 : 128);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<elem_t>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -257,16 +268,18 @@ __global__ void rope_cache_write_vec4_kernel(T* __restrict__ qkv, const int* __r
                                              const float* __restrict__ inv_freq, const int* __restrict__ slots,
                                              T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
                                              int head_dim, int page_size, int write_kv) {
-  chain_wait();
+  // Positions and slots are the step's metadata and the frequencies are constants: the angles are
+  // ready before the kernel that produces qkv has finished.
   extern __shared__ float trig[];            // cos[half], sin[half]
   const int t = blockIdx.x;
   const int half = head_dim / 2;
   const float pos = (float)positions[t];
   for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], trig + half + j, trig + j);
+  const int slot = (write_kv && slots) ? slots[t] : -1;
   __syncthreads();
+  chain_wait();
   const int row_width = (nq + 2 * nkv) * head_dim;
   T* row = qkv + (size_t)t * row_width;
-  const int slot = (write_kv && slots) ? slots[t] : -1;
   const int page = slot >= 0 ? slot / page_size : 0;
   const int offset = slot >= 0 ? slot % page_size : 0;
   const int per_head = half / 4;              // items per rotated head
