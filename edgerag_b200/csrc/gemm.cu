@@ -146,16 +146,22 @@ __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int NT, bool OUT_F32, int kSkWarps>   // NT: tiles of 8 rows of `a`
+// MODE 0: bfloat16 out; 1: float out; 2: gated (see erb_linear_skinny_glu): w holds N gate rows and
+// then N up rows, a block takes 8 gate rows as the first half of its 16 and the 8 up rows that go
+// with them as the second, so that after the reduction one thread holds g and u of an output and
+// writes silu(g) * u (both rounded to bfloat16 first, as if the product had been stored).
+template <int NT, int MODE, int kSkWarps>   // NT: tiles of 8 rows of `a`
 __global__ void __launch_bounds__(kSkWarps * 32, NT == 1 ? 32 / kSkWarps : 1)
 linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                      int M, int N, int K, int lda, int ldw, int ldo) {
+  constexpr bool OUT_F32 = MODE == 1;
+  constexpr bool GLU = MODE == 2;
   __shared__ float red[kSkWarps][NT][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
-  const int n0 = blockIdx.x * 16;
+  const int n0 = blockIdx.x * (GLU ? 8 : 16);
   const uint4* w_lo = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + r, N - 1) * ldw);
-  const uint4* w_hi = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + r + 8, N - 1) * ldw);
+  const uint4* w_hi = reinterpret_cast<const uint4*>(w + (size_t)(GLU ? N + min(n0 + r, N - 1) : min(n0 + r + 8, N - 1)) * ldw);
   const int chunks = K >> 3;                          // 16-byte chunks per row
   const int passes = (chunks + 3) >> 2;               // 4 chunks (32 k) per pass
   const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -216,6 +222,22 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
     for (int i = 0; i < 4; ++i) red[warp][t][lane][i] = acc[t][i];
   __syncthreads();
   // Accumulator layout: values 0, 1 belong to w row r, values 2, 3 to row r + 8; `a` rows 2j, 2j + 1.
+  if constexpr (GLU) {
+    for (int idx = threadIdx.x; idx < NT * 32 * 2; idx += kSkWarps * 32) {
+      const int t = idx / 64, l = (idx / 2) % 32, i = idx % 2;
+      float g = 0.f, u = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < kSkWarps; ++wv) { g += red[wv][t][l][i]; u += red[wv][t][l][i + 2]; }
+      const int n = n0 + (l >> 2);
+      const int m = t * 8 + (l & 3) * 2 + i;
+      if (n < N && m < M) {
+        g = __bfloat162float(__float2bfloat16_rn(g));
+        u = __bfloat162float(__float2bfloat16_rn(u));
+        reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+      }
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < NT * 32 * 4; idx += kSkWarps * 32) {
     const int t = idx / 128, l = (idx / 4) % 32, i = idx % 4;
     float sum = 0.f;
@@ -230,28 +252,32 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
   }
 }
 
-template <int NT>
-int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw, int ldo,
-                  int out_f32, cudaStream_t s) {
-  const unsigned blocks = (unsigned)((N + 15) / 16);
-  const __nv_bfloat16 *ap = (const __nv_bfloat16*)a, *wp = (const __nv_bfloat16*)w;
+template <int NT, int MODE>
+int launch_skinny_mode(const __nv_bfloat16* ap, const __nv_bfloat16* wp, void* out, int M, int N, int K, int lda,
+                       int ldw, int ldo, cudaStream_t s) {
+  const unsigned blocks = (unsigned)(MODE == 2 ? (N + 7) / 8 : (N + 15) / 16);
   if constexpr (NT == 1) {
     if (blocks <= 148 && K >= 4096) {           // at most one block per SM and long rows: 32 warps per block
-      if (out_f32) launch_chained(linear_skinny_kernel<NT, true, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
-      else launch_chained(linear_skinny_kernel<NT, false, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+      launch_chained(linear_skinny_kernel<NT, MODE, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
       return check_launch("linear_skinny");
     }
   }
   if constexpr (NT <= 2) {
     if (blocks < 2 * 148 && K >= 1024) {        // few blocks: twice the warps per block
-      if (out_f32) launch_chained(linear_skinny_kernel<NT, true, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
-      else launch_chained(linear_skinny_kernel<NT, false, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+      launch_chained(linear_skinny_kernel<NT, MODE, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
       return check_launch("linear_skinny");
     }
   }
-  if (out_f32) launch_chained(linear_skinny_kernel<NT, true, 8>, dim3(blocks), dim3(256), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
-  else launch_chained(linear_skinny_kernel<NT, false, 8>, dim3(blocks), dim3(256), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+  launch_chained(linear_skinny_kernel<NT, MODE, 8>, dim3(blocks), dim3(256), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
   return check_launch("linear_skinny");
+}
+
+template <int NT>
+int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw, int ldo,
+                  int out_f32, cudaStream_t s) {
+  const __nv_bfloat16 *ap = (const __nv_bfloat16*)a, *wp = (const __nv_bfloat16*)w;
+  if (out_f32) return launch_skinny_mode<NT, 1>(ap, wp, out, M, N, K, lda, ldw, ldo, s);
+  return launch_skinny_mode<NT, 0>(ap, wp, out, M, N, K, lda, ldw, ldo, s);
 }
 
 }  // namespace
@@ -270,5 +296,22 @@ ERB_EXPORT int erb_linear_skinny(const void* a, const void* w, void* out, int M,
   if (M <= 16) return launch_skinny<2>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
   if (M <= 32) return launch_skinny<4>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
   return launch_skinny<8>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+}
+
+// Gated product for the feed-forward of a decode step: w holds N gate rows and then N up rows
+// ([2N, K]); out[M, N] = silu(g) * u with g = a * gate^T and u = a * up^T, each rounded to bfloat16
+// before the gate (so the result equals erb_linear_skinny into a [M, 2N] buffer followed by the
+// gate kernel), 1 <= M <= 16.
+ERB_EXPORT int erb_linear_skinny_glu(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw,
+                                     int ldo, void* stream) {
+  if (M <= 0) return ERB_OK;
+  if (M > 16) return fail(ERB_ERR_UNSUPPORTED, "linear_skinny_glu: %d rows (at most 16)", M);
+  if (N <= 0 || K <= 0 || lda < K || ldw < K || ldo < N) return fail(ERB_ERR_ARG, "linear_skinny_glu: bad sizes");
+  if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15))
+    return fail(ERB_ERR_UNSUPPORTED, "linear_skinny_glu: K and the leading dimensions must be multiples of 8");
+  const __nv_bfloat16 *ap = (const __nv_bfloat16*)a, *wp = (const __nv_bfloat16*)w;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (M <= 8) return launch_skinny_mode<1, 2>(ap, wp, out, M, N, K, lda, ldw, ldo, s);
+  return launch_skinny_mode<2, 2>(ap, wp, out, M, N, K, lda, ldw, ldo, s);
 }
 #endif  // ERB_ELEM == 1

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "erb_linear": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_void_p, c_longlong, c_void_p],
     "erb_linear_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_linear_skinny_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_attention_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "erb_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -241,6 +242,28 @@ def linear_few_rows(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) ->
         raise KernelError("linear_few_rows: operands not supported")
     _call(_fn("gemm", "bfloat16", "erb_linear_skinny"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
           lda, k, ldo, int(out.dtype == torch.float32), _stream())
+
+
+def linear_glu_supported(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``linear_glu`` takes these operands: a handful of bfloat16 rows, 16-byte rows."""
+    lda = a.stride(0) if a.shape[0] > 1 else max(a.shape[1], a.stride(0))
+    return a.shape[0] <= SKINNY_MAX_ROWS and weight.shape[0] % 2 == 0 and linear_few_rows_supported(a, weight, lda)
+
+
+def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = silu(a @ gate^T) * (a @ up^T) for ``weight = [gate; up]`` of shape [2N, K], in one
+    launch; equal to ``linear`` into an [M, 2N] buffer followed by ``swiglu`` (each product is rounded
+    to bfloat16 before the gate)."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
+    _need(out, "out", torch.bfloat16, contiguous=False)
+    m, k = a.shape
+    n = weight.shape[0] // 2
+    if weight.shape[1] != k or out.shape != (m, n) or a.stride(1) != 1 or out.stride(1) != 1 or not linear_glu_supported(a, weight):
+        raise KernelError("linear_glu: shapes, strides or operands not supported")
+    lda = a.stride(0) if m > 1 else max(k, a.stride(0))
+    ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
+    _call(_fn("gemm", "bfloat16", "erb_linear_skinny_glu"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+          lda, k, ldo, _stream())
 
 
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -1,6 +1,7 @@
 """The gated feed-forward of the Llama decoder: ``down(silu(gate(x)) * up(x))``, no biases
 (edgerag/core/layers.py:332-341).  ``gate`` and ``up`` are stored as one matrix ``[Wg; Wu]`` so a
-single product feeds the gate kernel, which computes ``silu(g) * u`` in float32 and rounds once.
+single product feeds the gate kernel, which computes ``silu(g) * u`` in float32 and rounds once; for
+the few rows of a decode step the product and the gate are one kernel with the same result.
 """
 
 from __future__ import annotations
@@ -33,10 +34,13 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         n = x.shape[0]
-        gate_up = ctx.buf("ffn.gate_up", (n, 2 * self.intermediate), self.dtype)
-        kernels.linear(x, self.w_gate_up, gate_up)
         act = ctx.buf("ffn.act", (n, self.intermediate), self.dtype)
-        kernels.swiglu(gate_up, act)
+        if kernels.linear_glu_supported(x, self.w_gate_up):
+            kernels.linear_glu(x, self.w_gate_up, act)       # a few rows: product and gate in one kernel
+        else:
+            gate_up = ctx.buf("ffn.gate_up", (n, 2 * self.intermediate), self.dtype)
+            kernels.linear(x, self.w_gate_up, gate_up)
+            kernels.swiglu(gate_up, act)
         y = ctx.buf("ffn.out", (n, self.hidden), self.dtype)
         kernels.linear(act, self.w_down, y)
         return y

@@ -182,6 +182,28 @@ def test_linear_for_few_rows_streams_weights(k):
         assert k.launch_counts["library"] == before["library"] + int(not own)
 
 
+def test_gated_product_equals_product_then_gate(k):
+    """The decode step's gate/up product with the gate in its epilogue gives, bit for bit, what the
+    plain product into a [M, 2N] buffer followed by the gate kernel gives, and both follow the
+    formula silu(x Wg^T) * (x Wu^T); N no multiple of the 8 gate rows a block takes, K no multiple of a pass."""
+    for m, n, kk in ((1, 96, 64), (8, 8192 // 4, 2048), (5, 203, 1032), (16, 77, 264), (11, 1024, 4096)):
+        a = rand((m, kk), torch.bfloat16, 70 + m, 0.5)
+        w = rand((2 * n, kk), torch.bfloat16, 71 + m, 0.3)
+        assert k.linear_glu_supported(a, w)
+        both = torch.empty((m, 2 * n), dtype=torch.bfloat16, device="cuda")
+        k.linear(a, w, both)
+        two_steps = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        k.swiglu(both, two_steps)
+        fused = torch.full((m, n + 5), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :n]
+        k.linear_glu(a, w, fused)
+        assert torch.equal(fused, two_steps)
+        g, u = (a.double() @ w.double().T).split(n, dim=1)
+        want = torch.nn.functional.silu(g) * u
+        torch.testing.assert_close(fused.double(), want, atol=0.02 * (kk ** 0.5) / 8, rtol=0.02)
+    assert not k.linear_glu_supported(rand((17, 64), torch.bfloat16, 1), rand((32, 64), torch.bfloat16, 2))
+    assert not k.linear_glu_supported(rand((4, 64), torch.float32, 1), rand((32, 64), torch.float32, 2))
+
+
 # --- attention -------------------------------------------------------------------------------
 
 def paged_case(dtype, seed, nq, nkv, d, ps, ctx_lens, q_lens, poison=True):
