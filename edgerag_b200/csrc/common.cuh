@@ -112,6 +112,13 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return t;
 }
 
+// One rotary pair (x[j], x[j + half]) turned by the angle whose cosine and sine are given.  Written
+// with explicit roundings so that every kernel that rotates gives the same bits.
+__device__ __forceinline__ void rotate_pair(float a, float b, float cs, float sn, float& lo, float& hi) {
+  lo = __fmaf_rn(a, cs, -__fmul_rn(b, sn));
+  hi = __fmaf_rn(b, cs, __fmul_rn(a, sn));
+}
+
 // Chained launches.  Kernels that run back to back in the decode step are launched with
 // programmatic stream serialization: the next kernel's blocks may be scheduled while the previous
 // kernel drains, which hides the launch latency between the many short kernels of a step.  Every

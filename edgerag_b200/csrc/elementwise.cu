@@ -236,8 +236,7 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
       float sn, cs;
       sincosf(pos * inv_freq[j], &sn, &cs);
       const float a = Elem<T>::load(x + i0), b = Elem<T>::load(x + i1);
-      o0 = a * cs - b * sn;
-      o1 = b * cs + a * sn;
+      rotate_pair(a, b, cs, sn, o0, o1);
     } else {
       i0 = rot_dim + 2 * (j - half_rot); i1 = i0 + 1;
       o0 = Elem<T>::load(x + i0); o1 = Elem<T>::load(x + i1);
@@ -296,9 +295,7 @@ __global__ void rope_cache_write_vec4_kernel(T* __restrict__ qkv, const int* __r
       Pack4<T>::load(x + j + half, b);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float cs = trig[j + i], sn = trig[half + j + i];
-        lo[i] = a[i] * cs - b[i] * sn;
-        hi[i] = b[i] * cs + a[i] * sn;
+        rotate_pair(a[i], b[i], trig[j + i], trig[half + j + i], lo[i], hi[i]);
       }
       T* dst = x;
       if (head >= nq) dst = k_pages + (((size_t)page * nkv + (head - nq)) * page_size + offset) * head_dim;

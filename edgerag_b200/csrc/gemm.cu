@@ -150,18 +150,39 @@ __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t 
 // then N up rows, a block takes 8 gate rows as the first half of its 16 and the 8 up rows that go
 // with them as the second, so that after the reduction one thread holds g and u of an output and
 // writes silu(g) * u (both rounded to bfloat16 first, as if the product had been stored).
+// MODE 3 (see erb_linear_skinny_rope): w is [Wq; Wk; Wv]; a block of a q or k head takes 8 rows of
+// the head's first half and the 8 rows half a head further on, so that one thread holds both
+// elements of a rotary pair; it rotates them by the token's angle and writes q to `out` and k to
+// the token's cache slot.  Blocks of v heads take 16 neighbouring rows and write them to the slot.
+struct RopeArgs {
+  const int* positions;        // per row of `a`
+  const float* inv_freq;       // [head_dim / 2]
+  const int* slots;            // per row of `a`: page * page_size + offset, negative: write no k, v
+  __nv_bfloat16* k_pages;      // [page][kv head][offset][head_dim]
+  __nv_bfloat16* v_pages;
+  int nq, nkv, head_dim, page_size;
+};
+
 template <int NT, int MODE, int kSkWarps>   // NT: tiles of 8 rows of `a`
 __global__ void __launch_bounds__(kSkWarps * 32, NT == 1 ? 32 / kSkWarps : 1)
 linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
-                     int M, int N, int K, int lda, int ldw, int ldo) {
+                     int M, int N, int K, int lda, int ldw, int ldo, RopeArgs ra) {
   constexpr bool OUT_F32 = MODE == 1;
   constexpr bool GLU = MODE == 2;
+  constexpr bool ROPE = MODE == 3;
   __shared__ float red[kSkWarps][NT][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
   const int n0 = blockIdx.x * (GLU ? 8 : 16);
-  const uint4* w_lo = reinterpret_cast<const uint4*>(w + (size_t)min(n0 + r, N - 1) * ldw);
-  const uint4* w_hi = reinterpret_cast<const uint4*>(w + (size_t)(GLU ? N + min(n0 + r, N - 1) : min(n0 + r + 8, N - 1)) * ldw);
+  int row_lo = min(n0 + r, N - 1), row_hi = GLU ? N + min(n0 + r, N - 1) : min(n0 + r + 8, N - 1);
+  const int per_head = ROPE ? ra.head_dim / 16 : 1;            // blocks per head
+  const int rot_blocks = ROPE ? (ra.nq + ra.nkv) * per_head : 0;
+  if (ROPE && (int)blockIdx.x < rot_blocks) {
+    row_lo = ((int)blockIdx.x / per_head) * ra.head_dim + ((int)blockIdx.x % per_head) * 8 + r;
+    row_hi = row_lo + ra.head_dim / 2;
+  }
+  const uint4* w_lo = reinterpret_cast<const uint4*>(w + (size_t)row_lo * ldw);
+  const uint4* w_hi = reinterpret_cast<const uint4*>(w + (size_t)row_hi * ldw);
   const int chunks = K >> 3;                          // 16-byte chunks per row
   const int passes = (chunks + 3) >> 2;               // 4 chunks (32 k) per pass
   const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -222,6 +243,38 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
     for (int i = 0; i < 4; ++i) red[warp][t][lane][i] = acc[t][i];
   __syncthreads();
   // Accumulator layout: values 0, 1 belong to w row r, values 2, 3 to row r + 8; `a` rows 2j, 2j + 1.
+  if constexpr (ROPE) {
+    const int D = ra.head_dim, half = D / 2;
+    for (int idx = threadIdx.x; idx < NT * 32 * 2; idx += kSkWarps * 32) {
+      const int t = idx / 64, l = (idx / 2) % 32, i = idx % 2;
+      float lo = 0.f, hi = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < kSkWarps; ++wv) { lo += red[wv][t][l][i]; hi += red[wv][t][l][i + 2]; }
+      const int rr = l >> 2;
+      const int m = t * 8 + (l & 3) * 2 + i;
+      if (m >= M) continue;
+      lo = __bfloat162float(__float2bfloat16_rn(lo));           // the product as it would have been stored
+      hi = __bfloat162float(__float2bfloat16_rn(hi));
+      const int slot = ra.slots[m];
+      const size_t page = slot >= 0 ? slot / ra.page_size : 0, off = slot >= 0 ? slot % ra.page_size : 0;
+      if ((int)blockIdx.x < rot_blocks) {
+        const int head = (int)blockIdx.x / per_head, e = ((int)blockIdx.x % per_head) * 8 + rr;
+        float sn, cs, o0, o1;
+        sincosf((float)ra.positions[m] * ra.inv_freq[e], &sn, &cs);
+        rotate_pair(lo, hi, cs, sn, o0, o1);
+        __nv_bfloat16* dst = nullptr;
+        if (head < ra.nq) dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + (size_t)head * D;
+        else if (slot >= 0) dst = ra.k_pages + ((page * ra.nkv + (head - ra.nq)) * ra.page_size + off) * D;
+        if (dst) { dst[e] = __float2bfloat16_rn(o0); dst[e + half] = __float2bfloat16_rn(o1); }
+      } else if (slot >= 0) {
+        const int v0 = ((int)blockIdx.x - rot_blocks) * 16 + rr;      // element of the token's v row
+        __nv_bfloat16* dst = ra.v_pages + ((page * ra.nkv + v0 / D) * ra.page_size + off) * D + v0 % D;
+        dst[0] = __float2bfloat16_rn(lo);
+        dst[8] = __float2bfloat16_rn(hi);
+      }
+    }
+    return;
+  }
   if constexpr (GLU) {
     for (int idx = threadIdx.x; idx < NT * 32 * 2; idx += kSkWarps * 32) {
       const int t = idx / 64, l = (idx / 2) % 32, i = idx % 2;
@@ -254,21 +307,21 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
 
 template <int NT, int MODE>
 int launch_skinny_mode(const __nv_bfloat16* ap, const __nv_bfloat16* wp, void* out, int M, int N, int K, int lda,
-                       int ldw, int ldo, cudaStream_t s) {
+                       int ldw, int ldo, cudaStream_t s, RopeArgs ra = RopeArgs{}) {
   const unsigned blocks = (unsigned)(MODE == 2 ? (N + 7) / 8 : (N + 15) / 16);
   if constexpr (NT == 1) {
     if (blocks <= 148 && K >= 4096) {           // at most one block per SM and long rows: 32 warps per block
-      launch_chained(linear_skinny_kernel<NT, MODE, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+      launch_chained(linear_skinny_kernel<NT, MODE, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo, ra);
       return check_launch("linear_skinny");
     }
   }
   if constexpr (NT <= 2) {
     if (blocks < 2 * 148 && K >= 1024) {        // few blocks: twice the warps per block
-      launch_chained(linear_skinny_kernel<NT, MODE, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+      launch_chained(linear_skinny_kernel<NT, MODE, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo, ra);
       return check_launch("linear_skinny");
     }
   }
-  launch_chained(linear_skinny_kernel<NT, MODE, 8>, dim3(blocks), dim3(256), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo);
+  launch_chained(linear_skinny_kernel<NT, MODE, 8>, dim3(blocks), dim3(256), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo, ra);
   return check_launch("linear_skinny");
 }
 
@@ -296,6 +349,32 @@ ERB_EXPORT int erb_linear_skinny(const void* a, const void* w, void* out, int M,
   if (M <= 16) return launch_skinny<2>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
   if (M <= 32) return launch_skinny<4>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
   return launch_skinny<8>(a, w, out, M, N, K, lda, ldw, ldo, out_f32, s);
+}
+
+// The attention input projection of a decode step with the rotary encoding and the cache write in
+// its epilogue: w = [Wq; Wk; Wv] of shape [(nq + 2 nkv) * head_dim, K]; q is rotated and written to
+// out[M, >= nq * head_dim] (the k and v columns of `out` are not written), k is rotated and, with v,
+// written to each token's cache slot.  The products are rounded to bfloat16 before the rotation, so
+// the result equals erb_linear_skinny followed by the rotation kernel.  Full rotation only
+// (rot_dim == head_dim), head_dim a multiple of 16, 1 <= M <= 16.
+ERB_EXPORT int erb_linear_skinny_rope(const void* a, const void* w, void* out, int M, int K, int lda, int ldw, int ldo,
+                                      int nq, int nkv, int head_dim, const int* positions, const float* inv_freq,
+                                      const int* slots, void* k_pages, void* v_pages, int page_size, void* stream) {
+  if (M <= 0) return ERB_OK;
+  if (M > 16) return fail(ERB_ERR_UNSUPPORTED, "linear_skinny_rope: %d rows (at most 16)", M);
+  if (nq <= 0 || nkv <= 0 || head_dim <= 0 || head_dim % 16)
+    return fail(ERB_ERR_UNSUPPORTED, "linear_skinny_rope: head_dim %d must be a multiple of 16", head_dim);
+  const int N = (nq + 2 * nkv) * head_dim;
+  if (K <= 0 || lda < K || ldw < K || ldo < nq * head_dim || page_size <= 0 || !positions || !inv_freq || !slots ||
+      !k_pages || !v_pages)
+    return fail(ERB_ERR_ARG, "linear_skinny_rope: bad arguments");
+  if ((K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15))
+    return fail(ERB_ERR_UNSUPPORTED, "linear_skinny_rope: K and the leading dimensions must be multiples of 8");
+  const RopeArgs ra{positions, inv_freq, slots, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, nq, nkv, head_dim, page_size};
+  const __nv_bfloat16 *ap = (const __nv_bfloat16*)a, *wp = (const __nv_bfloat16*)w;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (M <= 8) return launch_skinny_mode<1, 3>(ap, wp, out, M, N, K, lda, ldw, ldo, s, ra);
+  return launch_skinny_mode<2, 3>(ap, wp, out, M, N, K, lda, ldw, ldo, s, ra);
 }
 
 // Gated product for the feed-forward of a decode step: w holds N gate rows and then N up rows

@@ -36,6 +36,8 @@ _SIGNATURES = {
                    c_void_p, c_longlong, c_void_p],
     "erb_linear_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_skinny_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_linear_skinny_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "erb_attention_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "erb_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -264,6 +266,38 @@ def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None
     ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
     _call(_fn("gemm", "bfloat16", "erb_linear_skinny_glu"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
           lda, k, ldo, _stream())
+
+
+def linear_rope_store_supported(a: torch.Tensor, weight: torch.Tensor, head_dim: int, rot_dim: int) -> bool:
+    """Whether ``linear_rope_store`` takes these operands: a handful of bfloat16 rows, full rotation,
+    head sizes in steps of 16."""
+    lda = a.stride(0) if a.shape[0] > 1 else max(a.shape[1], a.stride(0))
+    return (a.shape[0] <= SKINNY_MAX_ROWS and rot_dim == head_dim and head_dim % 16 == 0
+            and linear_few_rows_supported(a, weight, lda))
+
+
+def linear_rope_store(a: torch.Tensor, weight: torch.Tensor, qkv: torch.Tensor, positions: torch.Tensor,
+                      inv_freq: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, slots: torch.Tensor,
+                      k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int) -> None:
+    """``linear(a, [Wq; Wk; Wv], qkv)`` followed by ``rope_cache_write`` in one launch, for a few rows:
+    rotated q lands in ``qkv``'s q columns (its k and v columns are left as they are), rotated k and
+    v in the tokens' cache slots.  Same bits as the two kernels."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
+    _need(qkv, "qkv", torch.bfloat16, contiguous=False); _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32); _need(slots, "slots", torch.int32)
+    _need(k_pages, "k_pages", torch.bfloat16); _need(v_pages, "v_pages", torch.bfloat16)
+    m, k = a.shape
+    width = (n_q_heads + 2 * n_kv_heads) * head_dim
+    if (weight.shape != (width, k) or qkv.shape != (m, width) or a.stride(1) != 1 or qkv.stride(1) != 1
+            or positions.numel() < m or slots.numel() < m or inv_freq.numel() != head_dim // 2
+            or k_pages.shape[1:] != (n_kv_heads, page_size, head_dim) or v_pages.shape != k_pages.shape
+            or not linear_rope_store_supported(a, weight, head_dim, head_dim)):
+        raise KernelError("linear_rope_store: shapes, strides or operands not supported")
+    lda = a.stride(0) if m > 1 else max(k, a.stride(0))
+    ldo = qkv.stride(0) if m > 1 else max(width, qkv.stride(0))
+    _call(_fn("gemm", "bfloat16", "erb_linear_skinny_rope"), a.data_ptr(), weight.data_ptr(), qkv.data_ptr(), m, k,
+          lda, k, ldo, n_q_heads, n_kv_heads, head_dim, positions.data_ptr(), inv_freq.data_ptr(), slots.data_ptr(),
+          k_pages.data_ptr(), v_pages.data_ptr(), page_size, _stream())
 
 
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -64,13 +64,13 @@ class Attention(Mixer):
         n = x.shape[0]
         d = self.head_dim
         qkv = ctx.buf("attn.qkv", (n, self.q_width + 2 * self.kv_width), self.dtype)
-        kernels.linear(x, self.w_qkv, qkv)
         k_pages, v_pages = ctx.pages_of(call.cache_layer)
         group = ctx.group_of(call.cache_layer)
         write = call.writes_cache and self.own_kv
-        self.position.apply_and_store(qkv, ctx, self.n_q, self.n_kv, d,
-                                      (k_pages, v_pages) if write else None,
-                                      ctx.slots[group] if write else None)
+        pages, slots = ((k_pages, v_pages), ctx.slots[group]) if write else (None, None)
+        if not self.position.project_apply_store(x, self.w_qkv, qkv, ctx, self.n_q, self.n_kv, d, pages, slots):
+            kernels.linear(x, self.w_qkv, qkv)
+            self.position.apply_and_store(qkv, ctx, self.n_q, self.n_kv, d, pages, slots)
         out = ctx.buf("attn.out", (n, self.q_width), self.dtype)
         tables = ctx.block_tables[group]
         nd = ctx.n_decode

@@ -11,7 +11,9 @@ Interfaces (duck-typed; the base classes document them):
 * every part: ``weight_specs() -> list[WeightSpec]`` (names relative to the part's prefix) and
   ``load_weights(tensors: dict[str, Tensor])`` with those relative names;
 * ``Norm.forward(hidden, out, delta=None, rows=None, write_back=True)``;
-* ``PositionEncoding.apply_and_store(qkv, ctx, n_q_heads, n_kv_heads, head_dim, pages, slots)``;
+* ``PositionEncoding.apply_and_store(qkv, ctx, n_q_heads, n_kv_heads, head_dim, pages, slots)`` and,
+  optionally, ``project_apply_store(x, w_qkv, qkv, ctx, ...) -> bool`` (product, encoding and cache
+  write in one kernel, where the part has one);
 * ``Mixer.cache_spec()`` and ``Mixer.forward(x, ctx, call) -> Tensor``;
 * ``FeedForward.forward(x, ctx) -> Tensor``;
 * ``Block.forward(hidden, delta, ctx, call) -> delta`` (the update that is still to be added).
@@ -125,6 +127,16 @@ class PositionEncoding(Part):
         """Encode positions into q and k of ``qkv`` (rows: q heads, k heads, v heads) and, when
         ``pages`` is given, write the encoded k and v to the tokens' cache slots."""
         raise NotImplementedError
+
+
+    def project_apply_store(self, x: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, ctx: Any, n_q_heads: int,
+                            n_kv_heads: int, head_dim: int, pages: tuple[torch.Tensor, torch.Tensor] | None,
+                            slots: torch.Tensor | None) -> bool:
+        """Optional: the product ``qkv = x @ w_qkv^T``, the encoding and the cache write as one
+        kernel (only the q columns of ``qkv`` need to be valid afterwards).  Returns False, having
+        done nothing, when the part has no such kernel for these operands; the mixer then makes the
+        product itself and calls ``apply_and_store``."""
+        return False
 
 
 class Mixer(Part):

@@ -38,6 +38,14 @@ class RotaryHalves(PositionEncoding):
             qkv, ctx.positions, self.inv_freq, n_q_heads, n_kv_heads, head_dim, self.rot_dim,
             slots=slots, k_pages=k_pages, v_pages=v_pages, page_size=ctx.page_size)
 
+    def project_apply_store(self, x, w_qkv, qkv, ctx, n_q_heads, n_kv_heads, head_dim, pages, slots) -> bool:
+        """A few rows (a decode step): the rotation and the cache write ride in the product's epilogue."""
+        if pages is None or slots is None or not kernels.linear_rope_store_supported(x, w_qkv, head_dim, self.rot_dim):
+            return False
+        kernels.linear_rope_store(x, w_qkv, qkv, ctx.positions, self.inv_freq, n_q_heads, n_kv_heads, head_dim,
+                                  slots, pages[0], pages[1], ctx.page_size)
+        return True
+
 
 @register_part("position", "none")
 class NoPosition(PositionEncoding):

@@ -204,6 +204,39 @@ def test_gated_product_equals_product_then_gate(k):
     assert not k.linear_glu_supported(rand((4, 64), torch.float32, 1), rand((32, 64), torch.float32, 2))
 
 
+def test_projection_with_rotation_and_cache_write_equals_the_three_steps(k):
+    """The decode step's q/k/v product with the rotary encoding and the cache write in its epilogue
+    leaves, bit for bit, the q columns and the cache pages that the product, then the rotation
+    kernel leave; a token with a negative slot writes no key or value."""
+    for m, nq, nkv, d, kk, ps in ((1, 4, 2, 16, 64, 4), (8, 32, 32, 64, 2048, 16), (5, 9, 3, 48, 264, 8), (16, 6, 1, 128, 1032, 16)):
+        width = (nq + 2 * nkv) * d
+        a = rand((m, kk), torch.bfloat16, 80 + m, 0.5)
+        w = rand((width, kk), torch.bfloat16, 81 + m, 0.3)
+        inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))).cuda()
+        positions = torch.tensor([3 + 977 * i for i in range(m)], dtype=torch.int32).cuda()
+        n_pages = m + 2
+        slots = torch.tensor([((i * 5 + 1) % n_pages) * ps + (i * 3) % ps for i in range(m)], dtype=torch.int32)
+        if m > 2:
+            slots[2] = -1
+        slots = slots.cuda()
+        assert k.linear_rope_store_supported(a, w, d, d)
+        results = []
+        for fused in (False, True):
+            kp = torch.full((n_pages, nkv, ps, d), 7.0, dtype=torch.bfloat16, device="cuda")
+            vp = torch.full_like(kp, 7.0)
+            qkv = torch.zeros((m, width), dtype=torch.bfloat16, device="cuda")
+            if fused:
+                k.linear_rope_store(a, w, qkv, positions, inv_freq, nq, nkv, d, slots, kp, vp, ps)
+            else:
+                k.linear(a, w, qkv)
+                k.rope_cache_write(qkv, positions, inv_freq, nq, nkv, d, d, slots=slots, k_pages=kp, v_pages=vp, page_size=ps)
+            results.append((qkv[:, : nq * d].clone(), kp, vp))
+        for two, one in zip(*results):
+            assert torch.equal(two, one)
+        assert float(results[1][1].float().sub(7.0).abs().sum()) > 0      # something was written
+    assert not k.linear_rope_store_supported(rand((4, 64), torch.bfloat16, 1), rand((96, 64), torch.bfloat16, 2), 16, 8)
+
+
 # --- attention -------------------------------------------------------------------------------
 
 def paged_case(dtype, seed, nq, nkv, d, ps, ctx_lens, q_lens, poison=True):
