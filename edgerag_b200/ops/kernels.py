@@ -363,7 +363,7 @@ def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: 
     Measured on the decode step (24 layers, contexts of 8,192, batches of 1 to 16): best is the
     largest split that still fills most of one wave of blocks; a little more than one wave is worst
     (the few blocks of the second wave stream alone, far below the memory's bandwidth); from about
-    two waves on, the largest such split.  A function of the batch's size and of a power-of-two
+    two waves on, the largest such split, but no more than 1024 keys once there are many waves.  A function of the batch's size and of a power-of-two
     bound on its longest context only, so an eager step and a captured one make the same choice.
     """
     device = torch.cuda.current_device()
@@ -379,8 +379,8 @@ def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: 
     for s in fits:                       # most of one wave
         if 0.6 * slots <= blocks[s] <= slots:
             return s
-    for s in fits:                       # well beyond one wave
-        if blocks[s] >= 1.7 * slots:
+    for s in fits:                       # well beyond one wave: splits of 2048 only up to two waves (measured)
+        if blocks[s] >= 1.7 * slots and (s <= 1024 or blocks[s] <= 2 * slots):
             return s
     return fits[-1] if blocks[fits[-1]] < slots else min(fits, key=lambda s: abs(blocks[s] - slots))
 
