@@ -67,6 +67,8 @@ def decode_attention(a) -> dict:
     out = torch.empty_like(q)
     pos = torch.full((a.batch,), a.context - 1, dtype=torch.int32, device="cuda")
     tok = torch.arange(a.batch, dtype=torch.int32, device="cuda")
+    if a.split <= 0:        # as the engine chooses it: from the batch and a power-of-two bound on the context
+        a.split = kernels.choose_decode_split(a.batch, a.kv_heads, 1 << (a.context - 1).bit_length(), a.page)
     splits = (a.context - 1) // a.split + 1
     acc_n, ml_n = kernels.decode_scratch_floats(a.batch, a.heads, a.head_dim, splits)
     acc, ml = torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda")
@@ -80,7 +82,7 @@ def decode_attention(a) -> dict:
                                               split_keys=a.split)
     us = _time(fn, a.iters, a.warmup)
     nbytes = 2 * a.batch * a.context * a.kv_heads * a.head_dim * kp.element_size()
-    return {"case": "decode-attention", "kernel": a.kernel, "us": round(us, 2), "bytes": nbytes,
+    return {"case": "decode-attention", "kernel": a.kernel, "split": a.split, "us": round(us, 2), "bytes": nbytes,
             "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
             "status": int(status), "larger_than_l2": nbytes > 126e6}
 
@@ -144,7 +146,7 @@ def main(argv=None) -> int:
     d = sub.add_parser("decode-attention", parents=[common, att])
     d.add_argument("--batch", type=int, default=8)
     d.add_argument("--context", type=int, default=8192)
-    d.add_argument("--split", type=int, default=kernels.DECODE_SPLIT_KEYS)
+    d.add_argument("--split", type=int, default=0, help="keys per split; 0: the engine's choice for this batch")
     d.add_argument("--kernel", choices=["bulk", "general"], default="bulk")
     p = sub.add_parser("prefill-attention", parents=[common, att])
     p.add_argument("--tokens", type=int, default=2048)
