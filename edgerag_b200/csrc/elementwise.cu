@@ -101,7 +101,13 @@ template <> struct Pack4<__nv_bfloat16> {
   }
 };
 
-template <typename T>
+// The same with 16-byte accesses.  The order in which a row's squares are added is that of VT
+// "virtual threads" (element group g of the row belongs to virtual thread g % VT; warp trees over
+// 32 neighbouring virtual threads, then one tree over the warp sums), whatever the number of real
+// threads: a block of VT / R threads keeps R partial sums per thread, one per virtual thread it
+// stands for.  So the launch may use fewer, busier threads for many rows and more threads for the
+// few rows of a decode step, and a row's result does not depend on which.
+template <typename T, int R>
 __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
@@ -112,29 +118,47 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __r
   const int r = rows ? rows[o] : o;            // the step's metadata: not written by the kernel before
   float* h = hidden + (size_t)r * hidden_size;
   const T* d = delta ? delta + (size_t)r * hidden_size : nullptr;
+  const int threads = blockDim.x, vt = threads * R;
   // the norm's weight is a constant: this thread's first four are loaded before the wait
   const int i_first = threadIdx.x * 4;
   float w_first[4] = {0.f, 0.f, 0.f, 0.f};
   if (i_first < hidden_size) load4(weight + i_first, w_first);
   chain_wait();
-  float ss = 0.f;
-  for (int i = threadIdx.x * 4; i < hidden_size; i += blockDim.x * 4) {
-    float v[4];
-    load4(h + i, v);
-    if (d) {
-      float dv[4];
-      Pack4<T>::load(d + i, dv);
+  float ss[R];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] += dv[j];
-      if (write_back) *reinterpret_cast<float4*>(h + i) = make_float4(v[0], v[1], v[2], v[3]);
+  for (int q = 0; q < R; ++q) ss[q] = 0.f;
+  for (int base = 0; base < hidden_size; base += vt * 4) {
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const int i = base + (threadIdx.x + q * threads) * 4;
+      if (i >= hidden_size) continue;
+      float v[4];
+      load4(h + i, v);
+      if (d) {
+        float dv[4];
+        Pack4<T>::load(d + i, dv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] += dv[j];
+        if (write_back) *reinterpret_cast<float4*>(h + i) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+      *reinterpret_cast<float4*>(row_cache + i) = make_float4(v[0], v[1], v[2], v[3]);
+      ss[q] += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
     }
-    *reinterpret_cast<float4*>(row_cache + i) = make_float4(v[0], v[1], v[2], v[3]);
-    ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
   }
-  const float total = block_sum(ss, scratch);
+  // block_sum over the virtual threads
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = threads >> 5;
+#pragma unroll
+  for (int q = 0; q < R; ++q) ss[q] = warp_sum(ss[q]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int q = 0; q < R; ++q) scratch[warp + q * warps] = ss[q];
+  }
+  __syncthreads();
+  const float total = warp_sum(lane < warps * R ? scratch[lane] : 0.f);
   const float rs = rsqrtf(total / (float)hidden_size + eps);
   T* y = out + (size_t)o * hidden_size;
-  for (int i = threadIdx.x * 4; i < hidden_size; i += blockDim.x * 4) {
+  for (int i = threadIdx.x * 4; i < hidden_size; i += threads * 4) {
     float v[4], w[4];
     load4(row_cache + i, v);
     if (i == i_first) {
@@ -156,8 +180,8 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
   const size_t smem = (size_t)(hidden_size + 32) * sizeof(float);
   if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "add_rmsnorm: hidden_size %d too large", hidden_size);
   if (rows && write_back) return fail(ERB_ERR_ARG, "add_rmsnorm: row selection cannot write back");
-  // Threads per row depend on the width only, so a row's sum is formed in the same order whatever the
-  // batch; at 2048 and more, one pass of 16-byte loads per thread (the row's latency is paid once).
+  // The order of a row's sum depends on the width only (this many virtual threads), whatever the batch;
+  // at 2048 and more, one pass of 16-byte loads per thread (the row's latency is paid once).
   const int threads = hidden_size >= 2048 ? 512 : (hidden_size >= 512 ? 256 : 128);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<elem_t>,
@@ -167,13 +191,19 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
   const bool vec = hidden_size % 4 == 0 && !((uintptr_t)hidden & 15) && !((uintptr_t)delta & 7) &&
                    !((uintptr_t)out & 7) && !((uintptr_t)weight & 15);
   if (vec) {
+    // many rows of 2048 and more: half the threads, two virtual threads each (same sums, see the kernel)
+    const bool halve = threads == 512 && n_rows > 64;
     if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e = halve ? cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                            : cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "add_rmsnorm: %s", cudaGetErrorString(e));
     }
-    launch_chained(add_rmsnorm_vec4_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
-        (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+    if (halve)
+      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2>, dim3(n_rows), dim3(256), smem, (cudaStream_t)stream, (float*)hidden,
+          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+    else
+      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
+          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
   } else {
     launch_chained(add_rmsnorm_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
         (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);

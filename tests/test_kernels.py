@@ -80,6 +80,22 @@ def test_add_rmsnorm(k, dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [2048, 4096, 2052])
+def test_add_rmsnorm_gives_a_row_the_same_bits_in_any_batch(k, dtype, width):
+    """Wide rows are normed by more threads when the batch has few rows and by fewer, busier threads
+    when it has many; a row's result is the same bits either way."""
+    many = rand((200, width), torch.float32, 5, 2.0)
+    delta = rand((200, width), dtype, 6)
+    weight = rand((width,), torch.float32, 7).add_(1.0)
+    out_many = torch.empty((200, width), dtype=dtype, device="cuda")
+    h = many.clone()
+    k.add_rmsnorm(h, weight, out_many, 1e-5, delta=delta)
+    few, out_few = many[120:125].clone(), torch.empty((5, width), dtype=dtype, device="cuda")
+    k.add_rmsnorm(few, weight, out_few, 1e-5, delta=delta[120:125].clone())
+    assert torch.equal(out_few, out_many[120:125]) and torch.equal(few, h[120:125])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rot", [48, 32])
 def test_rope_cache_write(k, dtype, rot):
     nq, nkv, d, ps, n_pages = 6, 3, 48, 8, 7
