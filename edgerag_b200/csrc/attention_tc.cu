@@ -493,6 +493,10 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   const int warps_per_head = kDecWarps / hg;
   const int hh = warp / warps_per_head;                    // which head of the group this warp serves
   const int kvh = kvh0 + hh;
+  // The last group may hold fewer heads than hg (a head count that hg does not divide): the stage
+  // keeps its layout for hg heads, the copies bring the heads there are, the other warps idle.
+  const int hg_here = min(hg, nkv - kvh0);
+  const bool serves = hh < hg_here;
   const int t = token_of_seq[seq];
   const int pos = positions[t];
   const int begin = split * split_keys;
@@ -533,12 +537,13 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
     } else {
       // hg heads: whole pages (kb is a multiple of page_size), hg * page_size rows per copy
       const int n_pg = (ke - kb + page_size - 1) / page_size;
-      const uint32_t chunk_bytes = (uint32_t)(hg * page_size) * ROW;
+      const uint32_t slot_bytes = (uint32_t)(hg * page_size) * ROW;         // room of one page in the stage
+      const uint32_t chunk_bytes = (uint32_t)(hg_here * page_size) * ROW;   // what one page brings
       mbar_expect(bar, (uint32_t)n_pg * chunk_bytes * 2);
       for (int j = 0; j < n_pg; ++j) {
         const int page = s_pages[kb / page_size + j - first_page];
         const size_t src = ((size_t)page * nkv + kvh0) * page_size * D;
-        const uint32_t dst = (uint32_t)(s * STAGE_BYTES) + (uint32_t)j * chunk_bytes;
+        const uint32_t dst = (uint32_t)(s * STAGE_BYTES) + (uint32_t)j * slot_bytes;
         bulk_copy(sK + dst, k_pages + src, chunk_bytes, bar);
         bulk_copy(sV + dst, v_pages + src, chunk_bytes, bar);
       }
@@ -560,7 +565,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   float qr[R][8];
 #pragma unroll
   for (int g = 0; g < R; ++g) {
-    const __nv_bfloat16* qp = q + (size_t)t * q_row_stride + (size_t)(kvh * R + g) * D + chunk * 8;
+    const __nv_bfloat16* qp = q + (size_t)t * q_row_stride + (size_t)((serves ? kvh : kvh0) * R + g) * D + chunk * 8;
     float tmp[8];
     load8(qp, tmp);
 #pragma unroll
@@ -586,7 +591,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
     const int s = tile % kStages;
     if (ok && !mbar_wait(sBar + 8 * s, (tile / kStages) & 1)) ok = false;
     const int n_here = min(end - (begin + tile * STAGE_KEYS), STAGE_KEYS);
-    if (ok && key_in_stage < n_here) {
+    if (ok && serves && key_in_stage < n_here) {
       const uint8_t* kt = smem + s * STAGE_BYTES + row_offset + chunk * 16;
       const uint8_t* vt = kt + kStages * STAGE_BYTES;
       uint4 kraw[kKeysPerGroup];
@@ -683,7 +688,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
     if (tid == 0) atomicCAS(status, 0, 2000000 + (int)blockIdx.x);
     return;
   }
-  for (int idx = tid; idx < hg * R * D; idx += kDecThreads) {
+  for (int idx = tid; idx < hg_here * R * D; idx += kDecThreads) {
     const int head = idx / (R * D), g = (idx / D) % R, d = idx % D;
     const int w0 = head * warps_per_head;
     float m = -INFINITY;
@@ -739,18 +744,31 @@ attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const f
   }
 }
 
+// Heads per block of the bulk decode kernel: enough neighbouring kv heads that one page's rows make
+// a copy of about 8 KB, as long as whole pages tile a stage and the split.  A head count that this
+// does not divide gets one block for all its heads when they are at most 8 and their copy stays
+// within 16 KB (5 heads of 64 with 16-token pages: 10 KB copies instead of 2 KB ones), else a last
+// group with the heads that are left.
+int decode_head_group(int nkv, int head_dim, int page_size, int split_keys) {
+  const int stage_rows = kDecWarps * (32 / (head_dim / 8)) * kKeysPerGroup;
+  auto fits = [&](int hg) { return hg <= kDecWarps && (stage_rows / hg) % page_size == 0 && stage_rows / hg >= page_size; };
+  if (split_keys % page_size) return 1;
+  int hg = 1;
+  while (hg * 2 * page_size * head_dim * 2 <= 8192 && fits(hg * 2) && hg < nkv) hg *= 2;
+  if (nkv % hg) {
+    int all = 1;
+    while (all < nkv) all *= 2;
+    if (all > hg && fits(all) && nkv * page_size * head_dim * 2 <= 16384) hg = all;
+  }
+  return hg;
+}
+
 template <int D, int R>
 int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                        const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                        float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
                        int split_keys, float scale_log2, int* status, cudaStream_t s) {
-  // Heads per block: enough neighbouring kv heads that one page's rows make a copy of about 8 KB,
-  // as long as whole pages tile a stage and the split.
-  constexpr int STAGE_ROWS = kDecWarps * (32 / (D / 8)) * kKeysPerGroup;
-  int hg = 1;
-  while (hg < kDecWarps && hg * 2 * page_size * D * 2 <= 8192 && nkv % (hg * 2) == 0 &&
-         (STAGE_ROWS / (hg * 2)) % page_size == 0 && split_keys % page_size == 0)
-    hg *= 2;
+  const int hg = decode_head_group(nkv, D, page_size, split_keys);
   constexpr int STAGE_BYTES = kDecWarps * (32 / (D / 8)) * kKeysPerGroup * D * 2;
   const size_t smem = 2 * kStages * STAGE_BYTES + 64 + (size_t)kDecWarps * R * (D + 2) * sizeof(float) + 128 +
                       (size_t)(split_keys / page_size + 2) * sizeof(int);
@@ -762,7 +780,7 @@ int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, con
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_decode_bulk: %s", cudaGetErrorString(e));
     configured = smem;
   }
-  launch_chained(kern, dim3(dim3(max_splits, nkv / hg, n_seqs)), dim3(kDecThreads), smem, s, (const __nv_bfloat16*)q, q_row_stride,
+  launch_chained(kern, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kDecThreads), smem, s, (const __nv_bfloat16*)q, q_row_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, token_of_seq, positions,
       part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, status);
   return check_launch("attention_decode_bulk");
@@ -783,6 +801,13 @@ int dispatch_group(int r, const void* q, int q_row_stride, const void* k_pages, 
 }
 
 }  // namespace
+
+// Blocks per sequence and split of erb_attention_decode_bulk (groups of kv heads), for sizing decisions.
+ERB_EXPORT int erb_attention_decode_bulk_groups(int nkv, int head_dim, int page_size, int split_keys) {
+  if (nkv <= 0 || page_size <= 0 || (head_dim != 32 && head_dim != 64 && head_dim != 128)) return nkv > 0 ? nkv : 1;
+  const int hg = decode_head_group(nkv, head_dim, page_size, split_keys);
+  return (nkv + hg - 1) / hg;
+}
 
 // Same contract as the general decode entry point (scratch provided by the caller, splits at
 // absolute multiples of split_keys), for bfloat16 with head_dim 32 / 64 / 128, no window, at most

@@ -356,10 +356,10 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
 _sm_counts: dict[int, int] = {}
 
 
-def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int) -> int:
+def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int, head_dim: int = 64) -> int:
     """Keys per split for the decode kernels, from 128 to 2048.
 
-    The bulk kernel runs one block per (sequence, group of four kv heads, split), two blocks per SM.
+    The bulk kernel runs one block per (sequence, group of neighbouring kv heads, split), two blocks per SM.
     Measured on the decode step (24 layers, contexts of 8,192, batches of 1 to 16): best is the
     largest split that still fills most of one wave of blocks; a little more than one wave is worst
     (the few blocks of the second wave stream alone, far below the memory's bandwidth); from about
@@ -371,7 +371,7 @@ def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: 
     if sms is None:
         sms = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
     slots = 2 * sms
-    groups = max(1, n_kv_heads // 4)
+    groups = native.load("attention_tc", None).erb_attention_decode_bulk_groups(n_kv_heads, head_dim, page_size, 512)
     fits = [s for s in (2048, 1024, 512, 256, 128) if s % page_size == 0 or page_size % s == 0]
     if not fits:
         return DECODE_SPLIT_KEYS

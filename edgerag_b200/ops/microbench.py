@@ -68,7 +68,7 @@ def decode_attention(a) -> dict:
     pos = torch.full((a.batch,), a.context - 1, dtype=torch.int32, device="cuda")
     tok = torch.arange(a.batch, dtype=torch.int32, device="cuda")
     if a.split <= 0:        # as the engine chooses it: from the batch and a power-of-two bound on the context
-        a.split = kernels.choose_decode_split(a.batch, a.kv_heads, 1 << (a.context - 1).bit_length(), a.page)
+        a.split = kernels.choose_decode_split(a.batch, a.kv_heads, 1 << (a.context - 1).bit_length(), a.page, a.head_dim)
     splits = (a.context - 1) // a.split + 1
     acc_n, ml_n = kernels.decode_scratch_floats(a.batch, a.heads, a.head_dim, splits)
     acc, ml = torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda")

@@ -75,7 +75,7 @@ class Attention(Mixer):
         tables = ctx.block_tables[group]
         nd = ctx.n_decode
         if nd:
-            split = kernels.choose_decode_split(nd, self.n_kv, ctx.max_keys_bound(), ctx.page_size)
+            split = kernels.choose_decode_split(nd, self.n_kv, ctx.max_keys_bound(), ctx.page_size, d)
             max_splits = ctx.decode_splits(self.window, split)
             need_acc, need_ml = kernels.decode_scratch_floats(nd, self.n_q, d, max_splits)
             part_acc = ctx.buf("attn.part_acc", (need_acc,), torch.float32)
