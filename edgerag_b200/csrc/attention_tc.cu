@@ -16,8 +16,13 @@
 //
 // Every wait on an mbarrier is bounded: on a timeout the block records an error in *status,
 // skips the rest of its work, frees its TMEM and returns.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -801,6 +806,346 @@ int dispatch_group(int r, const void* q, int q_row_stride, const void* k_pages, 
 }
 
 }  // namespace
+
+// =============================================================================================
+// Decode attention for grouped query heads (2 to 8 query heads per kv head) on tensor cores.
+//
+// With several query heads per kv head the CUDA-core kernel above does its arithmetic once per
+// query head and key and falls behind the memory (3.4 TB/s at three heads per kv head).  Here the
+// query heads of a kv head are the rows of an mma.sync.m16n8k16 tile, so a key costs the same
+// whatever their number:
+//
+//   S[heads x 8 keys]   = Q[heads x 64] K^T       A = Q from registers, B = K rows via ldmatrix
+//   O[heads x 64]      += P[heads x 16 keys] V    A = P from the S registers, B = V via ldmatrix.trans
+//
+// The block structure is that of the kernel above: a block owns one (split of keys, group of hg
+// neighbouring kv heads, sequence); whole pages arrive in stages of 128 rows of K and of V, three
+// stages deep, completion counted by an mbarrier; a warp serves 16 keys of one kv head per stage;
+// partial results of warps and splits are merged exactly as above.  The difference in the data
+// path: pages are brought in by TMA tensor copies (cp.async.bulk.tensor.2d) through tensor maps
+// over the page pools with the 128-byte swizzle, so that the ldmatrix reads of 8 rows x 16 bytes
+// touch all banks.  bfloat16, head size 64, pages of a multiple of 8 tokens.
+// =============================================================================================
+namespace {
+
+constexpr int kGqaStageRows = 128;                         // rows (key, head) of K and of V per stage
+constexpr uint32_t kGqaStageBytes = kGqaStageRows * 128;   // 16 KB
+constexpr int kGqaStages = 3;
+constexpr int kGqaMaxHeads = 8;                            // query heads per kv head (rows 0..7 of the tile)
+
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, int row, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// d += a * b, a: 16 x 16 (rows 8..15 are zero: a1 = a3 = 0), b: 16 x 8
+__device__ __forceinline__ void mma_heads(float* d, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kDecThreads)
+attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const __grid_constant__ CUtensorMap map_k_last, const __grid_constant__ CUtensorMap map_v_last,
+                            const __nv_bfloat16* __restrict__ q, int q_row_stride,
+                            const int* __restrict__ block_tables, int max_pages,
+                            const int* __restrict__ token_of_seq, const int* __restrict__ positions,
+                            float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
+                            int nkv, int page_size, int split_keys, float scale_log2, int hg,
+                            int* __restrict__ status) {
+  constexpr int D = 64;
+  const int R = nq / nkv;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;            // the swizzle repeats every 1024 bytes
+  uint8_t* smem = smem_raw + (base - raw);
+  // layout: K stages | V stages | barriers | merge area | page ids
+  const uint32_t sK = base, sV = base + kGqaStages * kGqaStageBytes, sBar = sV + kGqaStages * kGqaStageBytes;
+  float* merge = reinterpret_cast<float*>(smem + 2 * kGqaStages * kGqaStageBytes + 64);   // [warps][R][D + 2]
+  int* s_pages = reinterpret_cast<int*>(merge + kDecWarps * R * (D + 2));
+
+  const int split = blockIdx.x, kvh0 = blockIdx.y * hg, seq = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warps_per_head = kDecWarps / hg;
+  const int hh = warp / warps_per_head, ws = warp % warps_per_head;
+  const int hg_here = min(hg, nkv - kvh0);
+  const bool serves = hh < hg_here;
+  const int stage_keys = kGqaStageRows / hg;               // keys of each head per stage
+  const int t = token_of_seq[seq];
+  const int pos = positions[t];
+  const int begin = split * split_keys;
+  const int end = min(pos + 1, begin + split_keys);
+  if (begin >= end) return;
+  const int* bt = block_tables + (size_t)seq * max_pages;
+  const int n_tiles = (end - begin + stage_keys - 1) / stage_keys;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kGqaStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sBar + 8 * s));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  const int first_page = begin / page_size;
+  const int n_pages = (end - 1) / page_size - first_page + 1;
+  for (int i = tid; i < n_pages; i += kDecThreads) s_pages[i] = bt[first_page + i];
+  __syncthreads();
+
+  const CUtensorMap* mk = hg_here == hg ? &map_k : &map_k_last;
+  const CUtensorMap* mv = hg_here == hg ? &map_v : &map_v_last;
+  const uint32_t page_slot = (uint32_t)(hg * page_size) * 128u;          // room of one page in a stage
+  const uint32_t page_bytes = (uint32_t)(hg_here * page_size) * 128u;    // what one page brings
+  auto issue = [&](int tile) {   // thread 0 only: whole pages, hg_here * page_size rows per copy
+    const int s = tile % kGqaStages;
+    const int kb = begin + tile * stage_keys, ke = min(end, kb + stage_keys);
+    const uint32_t bar = sBar + 8 * s;
+    const int n_pg = (ke - kb + page_size - 1) / page_size;
+    mbar_expect(bar, (uint32_t)n_pg * page_bytes * 2);
+    for (int j = 0; j < n_pg; ++j) {
+      const int page = s_pages[kb / page_size + j - first_page];
+      const int row = (page * nkv + kvh0) * page_size;
+      const uint32_t dst = (uint32_t)s * kGqaStageBytes + (uint32_t)j * page_slot;
+      tma_load_rows(sK + dst, mk, row, bar);
+      tma_load_rows(sV + dst, mv, row, bar);
+    }
+  };
+  // Tiles that end before the page of the new token hold nothing this step has written: they are
+  // asked for before the wait for the kernel that writes this step's keys and rotates q.
+  const int old_end = (pos / page_size) * page_size;
+  int issued = 0;
+  if (tid == 0) {
+    while (issued < kGqaStages && issued < n_tiles && min(end, begin + (issued + 1) * stage_keys) <= old_end) issue(issued++);
+  }
+  chain_wait();
+  if (tid == 0) {
+    for (int i = issued; i < kGqaStages && i < n_tiles; ++i) issue(i);
+  }
+
+  // Q of this warp's kv head as the A operand: row g = lane / 4 is query head g of the group.
+  const int g = lane >> 2, j = lane & 3;
+  uint32_t qa[4][2];
+  {
+    const bool real = serves && g < R;
+    const __nv_bfloat16* qp = q + (size_t)t * q_row_stride + (size_t)((real ? (kvh0 + hh) * R + g : 0)) * D;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      qa[ks][0] = real ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 2 * j) : 0u;
+      qa[ks][1] = real ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 2 * j + 8) : 0u;
+    }
+  }
+  float o[8][4];
+#pragma unroll
+  for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[nb][i] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;      // of row g; l_run is this lane's share of the row's sum
+
+  // Rows of this warp's two blocks of 8 keys inside a stage: key k of head hh sits in row
+  // ((k / page_size) * hg + hh) * page_size + k % page_size.
+  const int key0 = ws * 16;
+  auto row_of = [&](int k) { return ((k / page_size) * hg + hh) * page_size + k % page_size; };
+  const int row_a = row_of(key0), row_b = row_of(key0 + 8);
+  const int mi = lane >> 3, ri = lane & 7;   // ldmatrix: this lane gives the address of row ri of matrix mi
+
+  bool ok = true;
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int s = tile % kGqaStages;
+    if (ok && !mbar_wait(sBar + 8 * s, (tile / kGqaStages) & 1)) ok = false;
+    const int n_here = min(end - (begin + tile * stage_keys), stage_keys);
+    if (ok && serves && key0 < n_here) {
+      const uint32_t k_st = sK + (uint32_t)s * kGqaStageBytes, v_st = sV + (uint32_t)s * kGqaStageBytes;
+      // Rows past the last key may hold anything (unwritten slots, an earlier tile): their scores are
+      // masked below, and their values are zeroed here, since 0 * NaN would spoil the product.
+      if (key0 + 16 > n_here) {
+        for (int k = max(n_here, key0) * 8 + lane; k < (key0 + 16) * 8; k += 32) {
+          const int key = k >> 3, chunk = k & 7;
+          *reinterpret_cast<uint4*>(smem + (v_st - base) + row_of(key) * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+      // S for the two blocks of 8 keys
+      float sc[2][4];
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        const int row = (b ? row_b : row_a) + ri;
+        sc[b][0] = sc[b][1] = sc[b][2] = sc[b][3] = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t kf[4];
+          ldmatrix_x4(k_st + (uint32_t)row * 128u + (uint32_t)(((half * 4 + mi) ^ ri) << 4), kf);
+          mma_heads(sc[b], qa[half * 2][0], qa[half * 2][1], kf[0], kf[1]);
+          mma_heads(sc[b], qa[half * 2 + 1][0], qa[half * 2 + 1][1], kf[2], kf[3]);
+        }
+      }
+      // this lane: row g, keys key0 + 8 b + 2 j, + 1
+      float m_new = m_run;
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int key = key0 + 8 * b + 2 * j + i;
+          sc[b][i] = key < n_here ? sc[b][i] * scale_log2 : -INFINITY;
+          m_new = fmaxf(m_new, sc[b][i]);
+        }
+      m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 1));
+      m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 2));
+      // key0 < n_here: the row has at least one real key, so m_new is finite
+      const float a = exp2f(m_run - m_new);
+      float p[2][2], sum = 0.f;
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) { p[b][i] = exp2f(sc[b][i] - m_new); sum += p[b][i]; }
+      l_run = l_run * a + sum;
+      m_run = m_new;
+      const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]), pa2 = pack_bf16(p[1][0], p[1][1]);
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) { o[nb][0] *= a; o[nb][1] *= a; }
+      // O += P V over the 16 keys: matrices (keys 0..7 | 8..15) x (8 values of chunk nb | nb + 1)
+#pragma unroll
+      for (int nb = 0; nb < 8; nb += 2) {
+        uint32_t vf[4];
+        const int row = ((mi & 1) ? row_b : row_a) + ri;
+        ldmatrix_x4_trans(v_st + (uint32_t)row * 128u + (uint32_t)(((nb + (mi >> 1)) ^ ri) << 4), vf);
+        mma_heads(o[nb], pa0, pa2, vf[0], vf[1]);
+        mma_heads(o[nb + 1], pa0, pa2, vf[2], vf[3]);
+      }
+    }
+    __syncthreads();                                        // everyone is done with stage s
+    if (tid == 0 && ok && tile + kGqaStages < n_tiles) issue(tile + kGqaStages);
+  }
+
+  // The row's sum over its four lanes; then this warp's result for its query heads.
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (g < R) {
+    float* w = merge + (warp * R + g) * (D + 2);
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) { w[nb * 8 + 2 * j] = o[nb][0]; w[nb * 8 + 2 * j + 1] = o[nb][1]; }
+    if (j == 0) { w[D] = m_run; w[D + 1] = l_run; }
+  }
+  __syncthreads();
+  if (!ok) {
+    if (tid == 0) atomicCAS(status, 0, 2000000 + (int)blockIdx.x);
+    return;
+  }
+  for (int idx = tid; idx < hg_here * R * D; idx += kDecThreads) {
+    const int head = idx / (R * D), gq = (idx / D) % R, d = idx % D;
+    const int w0 = head * warps_per_head;
+    float m = -INFINITY;
+    for (int w = w0; w < w0 + warps_per_head; ++w) m = fmaxf(m, merge[(w * R + gq) * (D + 2) + D]);
+    float sum = 0.f, l = 0.f;
+    for (int w = w0; w < w0 + warps_per_head; ++w) {
+      const float mw = merge[(w * R + gq) * (D + 2) + D];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      sum += merge[(w * R + gq) * (D + 2) + d] * f;
+      l += merge[(w * R + gq) * (D + 2) + D + 1] * f;
+    }
+    const size_t slot = ((size_t)seq * nq + (kvh0 + head) * R + gq) * max_splits + split;
+    part_acc[slot * D + d] = sum;
+    if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+  }
+}
+
+// Tensor maps over a page pool [rows = pages * kv heads * page_size][64] with boxes of `box_rows`
+// rows, 128-byte swizzle.  Encoding is a host-side computation; the maps are kept per (pool, box).
+std::map<std::tuple<const void*, unsigned long long, unsigned>, CUtensorMap> g_maps;
+std::mutex g_maps_mutex;
+
+int pool_map(CUtensorMap* out, const void* pool, unsigned long long rows, unsigned box_rows) {
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  const auto key = std::make_tuple(pool, rows, box_rows);
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {64, rows};
+    const cuuint64_t strides[1] = {128};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = cuTensorMapEncodeTiled(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides,
+                                              box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ERB_ERR_CUDA, "attention_decode_gqa: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    if (g_maps.size() > 4096) g_maps.clear();
+    it = g_maps.emplace(key, m).first;
+  }
+  *out = it->second;
+  return ERB_OK;
+}
+
+}  // namespace
+
+// Whether erb_attention_decode_gqa takes these sizes (bfloat16 is implied).
+ERB_EXPORT int erb_attention_decode_gqa_supported(int nq, int nkv, int head_dim, int page_size, int split_keys) {
+  if (head_dim != 64 || nq <= 0 || nkv <= 0 || nq % nkv) return 0;
+  const int r = nq / nkv;
+  if (r < 2 || r > kGqaMaxHeads || page_size <= 0 || page_size % 8 || split_keys <= 0 || split_keys % page_size) return 0;
+  const int hg = decode_head_group(nkv, 64, page_size, split_keys);
+  return (kGqaStageRows / hg) % page_size == 0 && hg * page_size <= 256 && min(hg, nkv) * page_size <= 256;
+}
+
+// Same contract as erb_attention_decode_bulk, for 2 to 8 query heads per kv head of size 64;
+// n_pool_pages is the number of pages of k_pages / v_pages (the tensor maps cover the whole pool).
+ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
+                                        int n_pool_pages, const int* block_tables, int max_pages,
+                                        const int* token_of_seq, const int* positions, void* out, int out_row_stride,
+                                        float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv,
+                                        int head_dim, int page_size, int split_keys, float scale, int* status,
+                                        void* stream) {
+  if (n_seqs <= 0) return ERB_OK;
+  if (!erb_attention_decode_gqa_supported(nq, nkv, head_dim, page_size, split_keys))
+    return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: %d/%d heads of %d, pages of %d, splits of %d", nq, nkv,
+                head_dim, page_size, split_keys);
+  if (max_splits <= 0 || !part_acc || !part_ml || !status || n_pool_pages <= 0)
+    return fail(ERB_ERR_ARG, "attention_decode_gqa: bad arguments");
+  if (q_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127))
+    return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: q rows must be 16-byte aligned, pools 128-byte aligned");
+  if (n_seqs > 65535 || nkv > 65535) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: grid too large");
+  if (max_splits > kCombineMaxSplits)
+    return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: %d splits (at most %d)", max_splits, kCombineMaxSplits);
+  if ((unsigned long long)n_pool_pages * nkv * page_size > 0x7fffffffull)
+    return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: pool too large for 32-bit row coordinates");
+  const int hg = decode_head_group(nkv, 64, page_size, split_keys);
+  const int last = nkv % hg ? nkv % hg : hg;
+  const unsigned long long rows = (unsigned long long)n_pool_pages * nkv * page_size;
+  CUtensorMap mk, mv, mkl, mvl;
+  int rc;
+  if ((rc = pool_map(&mk, k_pages, rows, (unsigned)(hg * page_size))) || (rc = pool_map(&mv, v_pages, rows, (unsigned)(hg * page_size))) ||
+      (rc = pool_map(&mkl, k_pages, rows, (unsigned)(last * page_size))) || (rc = pool_map(&mvl, v_pages, rows, (unsigned)(last * page_size))))
+    return rc;
+  const int r = nq / nkv;
+  const size_t smem = 1024 + 2 * kGqaStages * kGqaStageBytes + 64 + (size_t)kDecWarps * r * (64 + 2) * sizeof(float) + 128 +
+                      (size_t)(split_keys / page_size + 2) * sizeof(int);
+  if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: split of %d keys in pages of %d", split_keys, page_size);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_gqa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_decode_gqa: %s", cudaGetErrorString(e));
+    configured = smem;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  launch_chained(attention_decode_gqa_kernel, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kDecThreads), smem, s,
+                 mk, mv, mkl, mvl, (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, token_of_seq, positions,
+                 part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, status);
+  if ((rc = check_launch("attention_decode_gqa"))) return rc;
+  launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
+      (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
+  return check_launch("attention_decode_bulk_combine");
+}
 
 // Blocks per sequence and split of erb_attention_decode_bulk (groups of kv heads), for sizing decisions.
 ERB_EXPORT int erb_attention_decode_bulk_groups(int nkv, int head_dim, int page_size, int split_keys) {

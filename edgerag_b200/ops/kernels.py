@@ -49,6 +49,9 @@ _SIGNATURES = {
     "erb_attention_decode_bulk": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_float, c_void_p, c_void_p],
+    "erb_attention_decode_gqa": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_float, c_void_p, c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
@@ -56,7 +59,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 2, "erb_linear": 0}
+_LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 2, "erb_attention_decode_gqa": 2, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16
 
 
@@ -442,6 +445,40 @@ def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
         raise KernelError("attention_decode_bulk: q/out inner stride must be 1")
     _call(_fn("attention_tc", None, "erb_attention_decode_bulk"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
+          positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
+          n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(), _stream())
+
+
+def decode_gqa_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_heads: int, n_kv_heads: int,
+                         page_size: int, split_keys: int, max_splits: int = 1) -> bool:
+    """Shapes the tensor-core decode kernel for grouped query heads takes: bfloat16, head size 64,
+    2 to 8 query heads per kv head, pages of a multiple of 8 tokens, no window."""
+    if dtype != torch.bfloat16 or window > 0 or max_splits > 64:
+        return False
+    return bool(native.load("attention_tc", None).erb_attention_decode_gqa_supported(
+        n_q_heads, n_kv_heads, head_dim, page_size, int(split_keys)))
+
+
+def attention_decode_gqa(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                         token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
+                         scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
+                         status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS) -> None:
+    """``attention_decode`` for several query heads per kv head on tensor cores: the query heads of a
+    kv head are the rows of one matrix tile, pages arrive by TMA tensor copies."""
+    _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pages, "k_pages", torch.bfloat16)
+    _need(v_pages, "v_pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
+    _need(token_of_seq, "token_of_seq", torch.int32); _need(positions, "positions", torch.int32)
+    _need(out, "out", torch.bfloat16, contiguous=False); _need(part_acc, "part_acc", torch.float32)
+    _need(part_ml, "part_ml", torch.float32); _need(status, "status", torch.int32)
+    n_seqs = token_of_seq.numel()
+    n_pages, nkv, page_size, d = k_pages.shape
+    need_acc, need_ml = decode_scratch_floats(n_seqs, n_q_heads, d, max_splits)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml or v_pages.shape != k_pages.shape:
+        raise KernelError("attention_decode_gqa: scratch too small or pools disagree")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention_decode_gqa: q/out inner stride must be 1")
+    _call(_fn("attention_tc", None, "erb_attention_decode_gqa"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
+          v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
           n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(), _stream())
 

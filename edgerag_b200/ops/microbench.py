@@ -74,7 +74,10 @@ def decode_attention(a) -> dict:
     acc, ml = torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     scale = a.head_dim ** -0.5
-    if a.kernel == "bulk":
+    if a.kernel == "gqa":
+        fn = lambda: kernels.attention_decode_gqa(q, kp, vp, tables, tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
+                                                  status, split_keys=a.split)
+    elif a.kernel == "bulk":
         fn = lambda: kernels.attention_decode_bulk(q, kp, vp, tables, tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
                                                    status, split_keys=a.split)
     else:
@@ -147,7 +150,7 @@ def main(argv=None) -> int:
     d.add_argument("--batch", type=int, default=8)
     d.add_argument("--context", type=int, default=8192)
     d.add_argument("--split", type=int, default=0, help="keys per split; 0: the engine's choice for this batch")
-    d.add_argument("--kernel", choices=["bulk", "general"], default="bulk")
+    d.add_argument("--kernel", choices=["bulk", "gqa", "general"], default="bulk")
     p = sub.add_parser("prefill-attention", parents=[common, att])
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--past", type=int, default=0)

@@ -80,7 +80,11 @@ class Attention(Mixer):
             need_acc, need_ml = kernels.decode_scratch_floats(nd, self.n_q, d, max_splits)
             part_acc = ctx.buf("attn.part_acc", (need_acc,), torch.float32)
             part_ml = ctx.buf("attn.part_ml", (need_ml,), torch.float32)
-            if kernels.decode_bulk_supported(self.dtype, d, self.window, self.n_q, self.n_kv, max_splits):
+            if kernels.decode_gqa_supported(self.dtype, d, self.window, self.n_q, self.n_kv, ctx.page_size, split, max_splits):
+                kernels.attention_decode_gqa(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
+                                             out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,
+                                             split_keys=split)
+            elif kernels.decode_bulk_supported(self.dtype, d, self.window, self.n_q, self.n_kv, max_splits):
                 kernels.attention_decode_bulk(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                               out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,
                                               split_keys=split)

@@ -371,6 +371,36 @@ def test_attention_decode_bulk_copies(k, nq, nkv, d, ps, split):
     torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
 
 
+@pytest.mark.parametrize("nq,nkv,ps,split", [(15, 5, 16, 512), (9, 3, 16, 1024), (6, 2, 8, 128), (8, 1, 16, 256),
+                                             (16, 8, 32, 512), (20, 10, 16, 2048), (24, 3, 64, 512), (4, 2, 128, 256)])
+def test_attention_decode_for_grouped_heads_on_tensor_cores(k, nq, nkv, ps, split):
+    """Several query heads per kv head as the rows of one tensor-core tile, pages brought in by TMA
+    tensor copies: lengths around stage, page and split edges, head groups with a smaller last
+    group, NaN in unwritten slots (masked keys must not reach the product)."""
+    dtype, d = torch.bfloat16, 64
+    assert k.decode_gqa_supported(dtype, d, 0, nq, nkv, ps, split)
+    ctx_lens = [1, 15, 16, 17, 63, 64, 65, 1300, 512, 513, 129, 2048]
+    case = paged_case(dtype, 190 + nq + ps, nq, nkv, d, ps, ctx_lens, [1] * len(ctx_lens))
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    n = len(ctx_lens)
+    max_splits = max((c - 1) // split + 1 for c in ctx_lens)
+    acc_n, ml_n = k.decode_scratch_floats(n, nq, d, max_splits)
+    part_acc = torch.full((acc_n,), float("nan"), device="cuda")
+    part_ml = torch.full((ml_n,), float("nan"), device="cuda")
+    out = torch.full((n, nq * d), float("nan"), dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tok = torch.arange(n, dtype=torch.int32).cuda()
+    k.attention_decode_gqa(dev["q"], dev["kp"], dev["vp"], dev["tables"], tok, dev["pos"], out, nq, scale,
+                           part_acc, part_ml, max_splits, status, split_keys=split)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    want = attention_reference(case, nq, nkv, d, scale)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+    assert not k.decode_gqa_supported(dtype, d, 0, 4, 4, ps, split)          # one query head per kv head: the other kernel
+    assert not k.decode_gqa_supported(dtype, 128, 0, nq, nkv, ps, split)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key(k, dtype):
     """One key far back, in the first page, gets a score that stands out: the output must be its value.
