@@ -832,6 +832,7 @@ constexpr int kGqaStageRows = 128;                         // rows (key, head) o
 constexpr uint32_t kGqaStageBytes = kGqaStageRows * 128;   // 16 KB
 constexpr int kGqaStages = 3;
 constexpr int kGqaMaxHeads = 8;                            // query heads per kv head (rows 0..7 of the tile)
+constexpr int kGqaThreads = kDecThreads + 32;               // eight multiplying warps and a copy warp
 
 __device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, int row, uint32_t bar) {
   asm volatile(
@@ -859,7 +860,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kDecThreads)
+__global__ void __launch_bounds__(kGqaThreads)
 attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __grid_constant__ CUtensorMap map_k_last, const __grid_constant__ CUtensorMap map_v_last,
                             const __nv_bfloat16* __restrict__ q, int q_row_stride,
@@ -876,6 +877,8 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   uint8_t* smem = smem_raw + (base - raw);
   // layout: K stages | V stages | barriers | merge area | page ids
   const uint32_t sK = base, sV = base + kGqaStages * kGqaStageBytes, sBar = sV + kGqaStages * kGqaStageBytes;
+  const uint32_t sEmpty = sBar + 8 * kGqaStages;           // consumers -> copy warp: the stage is free again
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + 2 * kGqaStages * kGqaStageBytes + 56);
   float* merge = reinterpret_cast<float*>(smem + 2 * kGqaStages * kGqaStageBytes + 64);   // [warps][R][D + 2]
   int* s_pages = reinterpret_cast<int*>(merge + kDecWarps * R * (D + 2));
 
@@ -896,19 +899,37 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < kGqaStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sBar + 8 * s));
+    for (int s = 0; s < kGqaStages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sBar + 8 * s));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sEmpty + 8 * s), "n"(kDecWarps));
+    }
+    *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   const int first_page = begin / page_size;
   const int n_pages = (end - 1) / page_size - first_page + 1;
-  for (int i = tid; i < n_pages; i += kDecThreads) s_pages[i] = bt[first_page + i];
+  for (int i = tid; i < n_pages; i += kGqaThreads) s_pages[i] = bt[first_page + i];
   __syncthreads();
+  // A wait that gives up when its own limit runs out or when another thread of the block has given up.
+  auto wait_for = [&](uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+      uint32_t done;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}\n"
+          : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+      if (done) return true;
+      if (*s_abort) return false;
+    }
+    *s_abort = 1;
+    return false;
+  };
 
   const CUtensorMap* mk = hg_here == hg ? &map_k : &map_k_last;
   const CUtensorMap* mv = hg_here == hg ? &map_v : &map_v_last;
   const uint32_t page_slot = (uint32_t)(hg * page_size) * 128u;          // room of one page in a stage
   const uint32_t page_bytes = (uint32_t)(hg_here * page_size) * 128u;    // what one page brings
-  auto issue = [&](int tile) {   // thread 0 only: whole pages, hg_here * page_size rows per copy
+  auto issue = [&](int tile) {   // one lane of the copy warp: whole pages, hg_here * page_size rows per copy
     const int s = tile % kGqaStages;
     const int kb = begin + tile * stage_keys, ke = min(end, kb + stage_keys);
     const uint32_t bar = sBar + 8 * s;
@@ -922,17 +943,23 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       tma_load_rows(sV + dst, mv, row, bar);
     }
   };
-  // Tiles that end before the page of the new token hold nothing this step has written: they are
-  // asked for before the wait for the kernel that writes this step's keys and rotates q.
-  const int old_end = (pos / page_size) * page_size;
-  int issued = 0;
-  if (tid == 0) {
-    while (issued < kGqaStages && issued < n_tiles && min(end, begin + (issued + 1) * stage_keys) <= old_end) issue(issued++);
+  if (warp == kDecWarps) {
+    // ---- the copy warp: one lane asks for tile after tile, as soon as the stage it goes into is free ----
+    // Tiles that end before the page of the new token hold nothing this step has written: they are
+    // asked for before the wait for the kernel that writes this step's keys and rotates q.
+    if (lane == 0) {
+      const int old_end = (pos / page_size) * page_size;
+      bool waited = false;
+      for (int tile = 0; tile < n_tiles; ++tile) {
+        if (!waited && min(end, begin + (tile + 1) * stage_keys) > old_end) { chain_wait(); waited = true; }
+        if (tile >= kGqaStages && !wait_for(sEmpty + 8 * (tile % kGqaStages), ((tile / kGqaStages) - 1) & 1)) break;
+        issue(tile);
+      }
+      if (!waited) chain_wait();
+    }
+    __syncwarp();
   }
   chain_wait();
-  if (tid == 0) {
-    for (int i = issued; i < kGqaStages && i < n_tiles; ++i) issue(i);
-  }
 
   // Q of this warp's kv head as the A operand: row g = lane / 4 is query head g of the group.
   const int g = lane >> 2, j = lane & 3;
@@ -963,7 +990,8 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   bool ok = true;
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int s = tile % kGqaStages;
-    if (ok && !mbar_wait(sBar + 8 * s, (tile / kGqaStages) & 1)) ok = false;
+    if (warp == kDecWarps) break;                           // the copy warp has nothing to multiply
+    if (ok && !wait_for(sBar + 8 * s, (tile / kGqaStages) & 1)) ok = false;
     const int n_here = min(end - (begin + tile * stage_keys), stage_keys);
     if (ok && serves && key0 < n_here) {
       const uint32_t k_st = sK + (uint32_t)s * kGqaStageBytes, v_st = sV + (uint32_t)s * kGqaStageBytes;
@@ -1024,25 +1052,25 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         mma_heads(o[nb + 1], pa0, pa2, vf[2], vf[3]);
       }
     }
-    __syncthreads();                                        // everyone is done with stage s
-    if (tid == 0 && ok && tile + kGqaStages < n_tiles) issue(tile + kGqaStages);
+    __syncwarp();                                           // this warp is done with stage s
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sEmpty + 8 * s) : "memory");
   }
 
   // The row's sum over its four lanes; then this warp's result for its query heads.
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-  if (g < R) {
+  if (warp < kDecWarps && g < R) {
     float* w = merge + (warp * R + g) * (D + 2);
 #pragma unroll
     for (int nb = 0; nb < 8; ++nb) { w[nb * 8 + 2 * j] = o[nb][0]; w[nb * 8 + 2 * j + 1] = o[nb][1]; }
     if (j == 0) { w[D] = m_run; w[D + 1] = l_run; }
   }
   __syncthreads();
-  if (!ok) {
+  if (*s_abort) {
     if (tid == 0) atomicCAS(status, 0, 2000000 + (int)blockIdx.x);
     return;
   }
-  for (int idx = tid; idx < hg_here * R * D; idx += kDecThreads) {
+  for (int idx = tid; idx < hg_here * R * D; idx += kGqaThreads) {
     const int head = idx / (R * D), gq = (idx / D) % R, d = idx % D;
     const int w0 = head * warps_per_head;
     float m = -INFINITY;
@@ -1138,7 +1166,7 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
   }
   cudaStream_t s = (cudaStream_t)stream;
   const float scale_log2 = scale * 1.4426950408889634f;
-  launch_chained(attention_decode_gqa_kernel, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kDecThreads), smem, s,
+  launch_chained(attention_decode_gqa_kernel, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kGqaThreads), smem, s,
                  mk, mv, mkl, mvl, (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, token_of_seq, positions,
                  part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, status);
   if ((rc = check_launch("attention_decode_gqa"))) return rc;
