@@ -374,7 +374,10 @@ def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: 
     if sms is None:
         sms = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
     slots = 2 * sms
-    groups = native.load("attention_tc", None).erb_attention_decode_bulk_groups(n_kv_heads, head_dim, page_size, 512)
+    if head_dim in (32, 64, 128):    # the sizes of the bulk-copy kernels: blocks per sequence and split as they group heads
+        groups = native.load("attention_tc", None).erb_attention_decode_bulk_groups(n_kv_heads, head_dim, page_size, 512)
+    else:                            # the general kernel (and no need to build the other library for it)
+        groups = n_kv_heads
     fits = [s for s in (2048, 1024, 512, 256, 128) if s % page_size == 0 or page_size % s == 0]
     if not fits:
         return DECODE_SPLIT_KEYS
