@@ -301,7 +301,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_strid
     // the row and reads its own part, which nobody else touches until the thread overwrites it with P.
     uint8_t* p_row = smem + (sP0 - base) + (j & 1) * kPBytes;
     *reinterpret_cast<float*>(p_row + swz(row, (half ^ 1) * 4)) = m_half;
-    __syncthreads();
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // only the two warps that share these rows
     const float m_tile = fmaxf(m_half, *reinterpret_cast<const float*>(p_row + swz(row, half * 4)));
     // The reference maximum moves only when the row's maximum grew by more than 2^8.
     float alpha = 1.f;
