@@ -471,7 +471,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
                              const int* __restrict__ token_of_seq, const int* __restrict__ positions,
                              float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
                              int nkv, int page_size, int split_keys, float scale_log2, int hg,
-                             int* __restrict__ status) {
+                             __nv_bfloat16* __restrict__ out, int out_row_stride, int* __restrict__ status) {
   // Everything up to chain_wait() below reads only what earlier steps or the host wrote (the batch's
   // metadata, keys and values of earlier tokens), so it runs while the kernel before this one (the
   // one that rotates q and writes this step's keys and values) is still at work.
@@ -705,6 +705,10 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
       sum += merge[(w * R + g) * (D + 2) + d] * f;
       l += merge[(w * R + g) * (D + 2) + D + 1] * f;
     }
+    if (max_splits == 1) {      // the only split: this is the result (what the combine kernel would make of it)
+      out[(size_t)t * out_row_stride + (size_t)((kvh0 + head) * R + g) * D + d] = __float2bfloat16_rn(sum * (1.f / l));
+      continue;
+    }
     const size_t slot = ((size_t)seq * nq + (kvh0 + head) * R + g) * max_splits + split;
     part_acc[slot * D + d] = sum;
     if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
@@ -772,7 +776,7 @@ template <int D, int R>
 int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                        const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                        float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
-                       int split_keys, float scale_log2, int* status, cudaStream_t s) {
+                       int split_keys, float scale_log2, void* out, int out_row_stride, int* status, cudaStream_t s) {
   const int hg = decode_head_group(nkv, D, page_size, split_keys);
   constexpr int STAGE_BYTES = kDecWarps * (32 / (D / 8)) * kKeysPerGroup * D * 2;
   const size_t smem = 2 * kStages * STAGE_BYTES + 64 + (size_t)kDecWarps * R * (D + 2) * sizeof(float) + 128 +
@@ -787,7 +791,7 @@ int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, con
   }
   launch_chained(kern, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kDecThreads), smem, s, (const __nv_bfloat16*)q, q_row_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, token_of_seq, positions,
-      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, status);
+      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, (__nv_bfloat16*)out, out_row_stride, status);
   return check_launch("attention_decode_bulk");
 }
 
@@ -795,11 +799,12 @@ template <int D>
 int dispatch_group(int r, const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                    const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                    float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
-                   int split_keys, float scale_log2, int* status, cudaStream_t s) {
+                   int split_keys, float scale_log2, void* out, int out_row_stride, int* status, cudaStream_t s) {
 #define ERB_R(RR)                                                                                              \
   case RR: return launch_decode_bulk<D, RR>(q, q_row_stride, k_pages, v_pages, block_tables, max_pages,        \
                                             token_of_seq, positions, part_acc, part_ml, max_splits, n_seqs, nq, \
-                                            nkv, page_size, split_keys, scale_log2, status, s);
+                                            nkv, page_size, split_keys, scale_log2, out, out_row_stride,       \
+                                            status, s);
   switch (r) { ERB_R(1) ERB_R(2) ERB_R(3) ERB_R(4) ERB_R(5) ERB_R(6) ERB_R(7) ERB_R(8) }
 #undef ERB_R
   return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: %d query heads per kv head (at most %d)", r, kMaxGroup);
@@ -868,7 +873,7 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ token_of_seq, const int* __restrict__ positions,
                             float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
                             int nkv, int page_size, int split_keys, float scale_log2, int hg,
-                            int* __restrict__ status) {
+                            __nv_bfloat16* __restrict__ out, int out_row_stride, int* __restrict__ status) {
   constexpr int D = 64;
   const int R = nq / nkv;
   extern __shared__ uint8_t smem_raw[];
@@ -1082,6 +1087,10 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       sum += merge[(w * R + gq) * (D + 2) + d] * f;
       l += merge[(w * R + gq) * (D + 2) + D + 1] * f;
     }
+    if (max_splits == 1) {      // the only split: this is the result (what the combine kernel would make of it)
+      out[(size_t)t * out_row_stride + (size_t)((kvh0 + head) * R + gq) * D + d] = __float2bfloat16_rn(sum * (1.f / l));
+      continue;
+    }
     const size_t slot = ((size_t)seq * nq + (kvh0 + head) * R + gq) * max_splits + split;
     part_acc[slot * D + d] = sum;
     if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
@@ -1168,8 +1177,9 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
   const float scale_log2 = scale * 1.4426950408889634f;
   launch_chained(attention_decode_gqa_kernel, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kGqaThreads), smem, s,
                  mk, mv, mkl, mvl, (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, token_of_seq, positions,
-                 part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, status);
-  if ((rc = check_launch("attention_decode_gqa"))) return rc;
+                 part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, (__nv_bfloat16*)out, out_row_stride,
+                 status);
+  if ((rc = check_launch("attention_decode_gqa")) || max_splits == 1) return rc;      // a single split wrote the result itself
   launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
       (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
   return check_launch("attention_decode_bulk_combine");
@@ -1206,16 +1216,16 @@ ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const 
   switch (head_dim) {
     case 32: rc = dispatch_group<32>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                      positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size, split_keys,
-                                     scale_log2, status, s); break;
+                                     scale_log2, out, out_row_stride, status, s); break;
     case 64: rc = dispatch_group<64>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                      positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size, split_keys,
-                                     scale_log2, status, s); break;
+                                     scale_log2, out, out_row_stride, status, s); break;
     case 128: rc = dispatch_group<128>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                        positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size,
-                                       split_keys, scale_log2, status, s); break;
+                                       split_keys, scale_log2, out, out_row_stride, status, s); break;
     default: return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: head_dim %d (takes 32, 64, 128)", head_dim);
   }
-  if (rc) return rc;
+  if (rc || max_splits == 1) return rc;      // a single split wrote the result itself
   launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
       (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
   return check_launch("attention_decode_bulk_combine");

@@ -450,6 +450,8 @@ def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
           n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(), _stream())
+    if max_splits == 1:
+        launch_counts["own"] -= 1       # a single split writes the result itself: no second kernel
 
 
 def decode_gqa_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_heads: int, n_kv_heads: int,
@@ -484,6 +486,8 @@ def attention_decode_gqa(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
           v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
           n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(), _stream())
+    if max_splits == 1:
+        launch_counts["own"] -= 1       # a single split writes the result itself: no second kernel
 
 
 def prefill_tc_supported(dtype: torch.dtype, head_dim: int, window: int) -> bool:

@@ -344,12 +344,12 @@ def test_attention_decode(k, dtype, nq, nkv, d, ps, window, split):
                                                (2, 2, 32, 64, 256), (5, 5, 64, 24, 512), (8, 8, 64, 16, 512),
                                                (16, 8, 64, 8, 512), (4, 4, 128, 16, 256), (15, 5, 64, 16, 512),
                                                (9, 3, 64, 16, 1024), (10, 10, 64, 16, 512), (6, 6, 64, 16, 256),
-                                               (7, 7, 32, 16, 512), (3, 3, 128, 16, 2048)])
+                                               (7, 7, 32, 16, 512), (3, 3, 128, 16, 2048), (4, 4, 64, 16, 2048)])
 def test_attention_decode_bulk_copies(k, nq, nkv, d, ps, split):
     """The decode kernel that streams pages with bulk asynchronous copies: lengths around stage and
     split edges, grouped heads, head counts that the heads per block do not divide (a last group
     with fewer heads, or one block for 5 or 6 heads), page sizes that do and do not divide a stage,
-    NaN in unwritten slots."""
+    a single split (the kernel then writes the result itself), NaN in unwritten slots."""
     dtype = torch.bfloat16
     ctx_lens = [1, 63, 64, 65, 1300, 512, 513, 129]
     case = paged_case(dtype, 90 + d + ps, nq, nkv, d, ps, ctx_lens, [1] * len(ctx_lens))
