@@ -15,7 +15,8 @@ of 8192 tokens.  A "step" is one decode step of the whole batch.
 * ``prefill``: one step with a portion of 2,048 prompt tokens.
 * ``roofline``: bytes the decode step has to read (every weight once, the cache of the live
   requests) over its time, against the measured copy bandwidth.
-* ``points``: decode throughput at batch 1 and 64 with the same context.
+* ``points``: decode throughput at batch 1 and 64 with the same context, and at batch 1, 8 and 64
+  with a short context of 640 tokens (``decode_b8_ctx640`` ...), where the weights dominate the bytes.
 
 The step's inputs (3.4 GB of weights, 12.9 GB of cache at batch 8) are far larger than the 126 MB
 L2, so no flush is needed between timed iterations.  ``--impl reference`` runs the unmodified
