@@ -458,8 +458,8 @@ def decode_gqa_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_hea
                          page_size: int, split_keys: int, max_splits: int = 1) -> bool:
     """Shapes the tensor-core decode kernel for grouped query heads takes: bfloat16, head size 64,
     2 to 8 query heads per kv head, pages of a multiple of 8 tokens, no window."""
-    if dtype != torch.bfloat16 or window > 0 or max_splits > 64:
-        return False
+    if dtype != torch.bfloat16 or window > 0 or max_splits > 64 or head_dim != 64 or n_q_heads == n_kv_heads:
+        return False        # (answered here so that other models need not build the tensor-core library)
     return bool(native.load("attention_tc", None).erb_attention_decode_gqa_supported(
         n_q_heads, n_kv_heads, head_dim, page_size, int(split_keys)))
 
