@@ -3,6 +3,7 @@
     python -m edgerag_b200.ops.microbench decode-attention --batch 8 --context 8192
     python -m edgerag_b200.ops.microbench prefill-attention --tokens 2048
     python -m edgerag_b200.ops.microbench linear --m 8 --n 6144 --k 2048
+    python -m edgerag_b200.ops.microbench step-kernels --layers 4 --batch 8 --context 8192 --iters 4
 
 Each case builds random inputs larger than the 126 MB L2 where the real workload is (or says that
 it is not), runs warm-up launches, then times ``--iters`` launches replayed from one CUDA graph with
@@ -133,6 +134,63 @@ def linear(a) -> dict:
             "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4), "tflops": round(flops / us / 1e6, 2)}
 
 
+def step_kernels(a) -> dict:
+    """Which kernels a step's time goes to: the SmolVLM-2.2B layer sizes with ``--layers`` layers, a
+    prefill of ``--tokens`` tokens and decode steps of ``--batch`` sequences at ``--context``, run
+    eagerly under the CUDA activity tracer without chained launches (so that a kernel's time is its
+    own).  The microseconds are per launch and carry the tracer's overhead: read them as shares."""
+    import os
+
+    os.environ["EDGERAG_B200_NO_CHAIN"] = "1"          # read when the first library launches a kernel
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..engine.engine import Engine, EngineOptions
+    from ..engine.step import StepEntry
+
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": a.layers, "hidden_size": 2048,
+           "num_attention_heads": a.heads, "num_key_value_heads": a.kv_heads, "head_dim": 64, "intermediate_size": 8192,
+           "vocab_size": 49155, "rope_theta": 273768.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+           "hidden_act": "silu", "max_position_embeddings": 8192, "pad_token_id": 0}
+    eng = Engine.from_config(cfg, 0, 0.02, EngineOptions(
+        dtype="bfloat16", block_size=16, num_blocks=a.batch * (a.context // 16 + 2) + a.tokens // 16 + 64,
+        max_batch_size=a.batch + 2, chunk_size=a.tokens, max_step_tokens=a.tokens + a.batch, max_model_len=a.context + 8,
+        cuda_graphs=False))
+    r = eng.runner
+    ids = torch.randint(0, 49155, (a.tokens,)).tolist()
+
+    def table(prof, launches_of):
+        rows = [(e.key, e.device_time_total / max(1, e.count), e.count) for e in prof.key_averages() if e.device_time_total > 0]
+        total = sum(us * n for _, us, n in rows)
+        rows.sort(key=lambda x: -x[1] * x[2])
+        return {"total_us_per_" + launches_of[0]: round(total / launches_of[1], 1),
+                "kernels": [{"name": k[:70], "us": round(us, 2), "calls": n, "share": round(us * n / total, 3)} for k, us, n in rows[:12]]}
+
+    def prefill(name):
+        r.admit(name)
+        r.step([StepEntry(name, tokens=ids, want=[a.tokens - 1])])
+        r.release(name)
+
+    prefill("w0")
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as p1:
+        prefill("w1")
+        torch.cuda.synchronize()
+    names = [f"d{i}" for i in range(a.batch)]
+    for n in names:
+        r.admit(n)
+        eng.cache.grow(n, a.context - 64)
+        eng.cache.advance(n, a.context - 64)
+    for _ in range(3):
+        r.step([StepEntry(n, tokens=[5], want=[0]) for n in names])
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as p2:
+        for _ in range(a.iters):
+            r.step([StepEntry(n, tokens=[5], want=[0]) for n in names])
+        torch.cuda.synchronize()
+    return {"case": "step-kernels", "layers": a.layers, "batch": a.batch, "context": a.context, "tokens": a.tokens,
+            "prefill": table(p1, ("step", 1)), "decode": table(p2, ("step", a.iters))}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="edgerag_b200.ops.microbench", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -160,11 +218,19 @@ def main(argv=None) -> int:
     g.add_argument("--n", type=int, default=6144)
     g.add_argument("--k", type=int, default=2048)
     g.add_argument("--out32", action="store_true")
+    k = sub.add_parser("step-kernels", parents=[common])
+    k.add_argument("--layers", type=int, default=4)
+    k.add_argument("--batch", type=int, default=8)
+    k.add_argument("--context", type=int, default=8192)
+    k.add_argument("--tokens", type=int, default=2048)
+    k.add_argument("--heads", type=int, default=32)
+    k.add_argument("--kv-heads", type=int, default=32)
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
-    fn = {"decode-attention": decode_attention, "prefill-attention": prefill_attention, "linear": linear}[a.case]
+    fn = {"decode-attention": decode_attention, "prefill-attention": prefill_attention, "linear": linear,
+          "step-kernels": step_kernels}[a.case]
     print(json.dumps(fn(a)))
     return 0
 
