@@ -164,7 +164,7 @@ struct RopeArgs {
 };
 
 template <int NT, int MODE, int kSkWarps>   // NT: tiles of 8 rows of `a`
-__global__ void __launch_bounds__(kSkWarps * 32, NT == 1 ? 32 / kSkWarps : 1)
+__global__ void __launch_bounds__(kSkWarps * 32, NT <= 2 ? 32 / kSkWarps : 1)
 linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, void* __restrict__ out,
                      int M, int N, int K, int lda, int ldw, int ldo, RopeArgs ra) {
   constexpr bool OUT_F32 = MODE == 1;
@@ -309,7 +309,7 @@ template <int NT, int MODE>
 int launch_skinny_mode(const __nv_bfloat16* ap, const __nv_bfloat16* wp, void* out, int M, int N, int K, int lda,
                        int ldw, int ldo, cudaStream_t s, RopeArgs ra = RopeArgs{}) {
   const unsigned blocks = (unsigned)(MODE == 2 ? (N + 7) / 8 : (N + 15) / 16);
-  if constexpr (NT == 1) {
+  if constexpr (NT <= 2) {
     if (blocks <= 148 && K >= 4096) {           // at most one block per SM and long rows: 32 warps per block
       launch_chained(linear_skinny_kernel<NT, MODE, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo, ra);
       return check_launch("linear_skinny");
