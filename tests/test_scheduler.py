@@ -63,6 +63,36 @@ def test_eos_stops_and_reports_stop():
     assert r.finish_reason == "stop" and r.generated_token_ids == [9, 5]
 
 
+def test_a_step_launched_ahead_for_a_request_that_stopped_is_dropped():
+    """The engine may launch the step that follows before it has read this step's tokens.  If a
+    request turns out to have stopped on its stop token, the entry of the step launched ahead is
+    skipped when that step is committed: no token appended, nothing counted, nothing freed twice."""
+    from edgerag_b200.engine.scheduler import ScheduledEntry
+
+    s, cache = make(prefill_chunk_size=8, max_batch_size=4, eos_token_id=9)
+    a, b = req("a", 5, new=6), req("b", 3, new=6)
+    s.add_request(a), s.add_request(b)
+    run_step(s, cache)                        # a's prompt and its first token
+    run_step(s, cache)                        # a decodes, b's prompt
+    cur = s.schedule()                        # both decode
+    assert [e.request.request_id for e in cur.entries] == ["a", "b"] and all(e.is_decode for e in cur.entries)
+    for e in cur.entries:
+        cache.grow(e.request.request_id, 1), cache.advance(e.request.request_id, 1)
+    ahead = Batch(cur.step + 1, [ScheduledEntry(e.request, e.start + 1, 1, False, True) for e in cur.entries])
+    for e in ahead.entries:                   # launched before cur's tokens are known
+        cache.grow(e.request.request_id, 1), cache.advance(e.request.request_id, 1)
+    done = s.update(cur, {"a": 9, "b": 7})    # a stops on its stop token
+    assert done == [a] and a.finish_reason == "stop" and "a" not in cache.requests
+    before = (list(a.generated_token_ids), s.stats.decode_tokens, s.stats.finished)
+    s.update(ahead, {"a": 5, "b": 8})
+    assert (list(a.generated_token_ids), s.stats.finished) == (before[0], before[2])
+    assert s.stats.decode_tokens == before[1] + 1 and b.generated_token_ids[-2:] == [7, 8]
+    cache.check_invariants()
+    while s.has_work:
+        run_step(s, cache)
+    assert cache.free_pages() == [32]
+
+
 def test_decodes_first_one_prefill_per_step_fifo_admission():
     s, cache = make(num_pages=64, prefill_chunk_size=4, max_batch_size=3, max_prefills_per_step=1)
     a, b, c, d = req("a", 2, 8), req("b", 9, 8), req("c", 3, 8), req("d", 3, 8)
