@@ -125,7 +125,7 @@ def linear(a) -> dict:
 
     def fn():
         state["i"] = (state["i"] + 1) % reps
-        kernels.linear(x, ws[state["i"]], out)
+        (kernels.linear_few_rows if a.few_rows else kernels.linear)(x, ws[state["i"]], out)
 
     us = _time(fn, a.iters, a.warmup)
     nbytes = a.n * a.k * x.element_size() + a.m * a.k * x.element_size() + out.numel() * out.element_size()
@@ -218,6 +218,7 @@ def main(argv=None) -> int:
     g.add_argument("--n", type=int, default=6144)
     g.add_argument("--k", type=int, default=2048)
     g.add_argument("--out32", action="store_true")
+    g.add_argument("--few-rows", action="store_true", help="force the weight-streaming kernel (up to 64 rows)")
     k = sub.add_parser("step-kernels", parents=[common])
     k.add_argument("--layers", type=int, default=4)
     k.add_argument("--batch", type=int, default=8)
