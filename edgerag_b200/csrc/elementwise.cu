@@ -108,7 +108,8 @@ template <> struct Pack4<__nv_bfloat16> {
 // stands for.  So the launch may use fewer, busier threads for many rows and more threads for the
 // few rows of a decode step, and a row's result does not depend on which.
 template <typename T, int R>
-__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
+__global__ void __launch_bounds__(512, 4)   // 32 registers: the SM's 2,048 threads stay resident
+add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
                                         int write_back) {
