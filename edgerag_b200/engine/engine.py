@@ -17,7 +17,7 @@ import json
 import time
 from dataclasses import dataclass, field
 from pathlib import Path
-from typing import Any
+from typing import Any, Iterator
 
 import torch
 
@@ -320,6 +320,17 @@ class Engine:
                 except OutOfPagesError:
                     pass        # nothing was changed; the scheduler decides after this step
         return self._collect(cur)
+
+    def stream(self) -> "Iterator[TokenEvent]":
+        """Run steps while there is work and yield every generated token as soon as the host has it
+        (the reference's ``InferenceEngine.stream``, edgerag/serve/engine.py:256-281, without the
+        thread: the caller's loop drives the engine).  Requests may be added while iterating."""
+        while self.has_work:
+            before = self.scheduler.step_index
+            events = self.step()
+            yield from events
+            if not events and self.scheduler.step_index == before and not self.scheduler.running:
+                return      # nothing could be scheduled: what is left waits for pages that never come
 
     def generate(self, prompts: list[list[int]] | None = None, sampling: SamplingParams | list[SamplingParams] | None = None,
                  prompt_embeds: list[torch.Tensor | None] | None = None) -> list[list[int]]:

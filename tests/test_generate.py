@@ -233,3 +233,25 @@ def test_lookahead_changes_no_token(model_folders):
     assert sorted(runs[True][0]) == sorted(runs[False][0])
     for rid in {e[0] for e in runs[True][0]}:         # each request's events in order, with and without
         assert [e for e in runs[True][0] if e[0] == rid] == [e for e in runs[False][0] if e[0] == rid]
+
+
+def test_stream_yields_tokens_as_they_come(model_folders):
+    """``Engine.stream`` yields every token with its request and index, in order per request, a request
+    added half-way joins in, and the tokens are those of ``generate``."""
+    from edgerag_b200 import Engine, SamplingParams
+
+    folder = model_folders("a", "float32", std=0.2)
+    cfg = plain.read_config(folder)
+    prompts = [helpers.random_sequence(cfg["vocab"], n, 700 + n) for n in (11, 29, 6)]
+    whole = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=64, max_batch_size=4)
+    want = whole.generate(prompts, SamplingParams(max_new_tokens=12))
+    engine = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=64, max_batch_size=4)
+    ids = [engine.add_request(p, SamplingParams(max_new_tokens=12)) for p in prompts[:2]]
+    got: dict[str, list[int]] = {}
+    for n, ev in enumerate(engine.stream()):
+        assert ev.index == len(got.setdefault(ev.request_id, []))
+        got[ev.request_id].append(ev.token_id)
+        assert ev.finished == (len(got[ev.request_id]) == 12)
+        if n == 5:
+            ids.append(engine.add_request(prompts[2], SamplingParams(max_new_tokens=12)))
+    assert [got[i] for i in ids] == want and not engine.has_work
