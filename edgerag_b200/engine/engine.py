@@ -214,6 +214,16 @@ class Engine:
         self.scheduler.add_request(request)
         return rid
 
+    def abort(self, request_id: str, reason: str = "aborted") -> bool:
+        """Stop a request wherever it is (queued, in a prompt, decoding, or in a step that is on the
+        device): its pages and slot are free at once; a token that a launched step still produces for
+        it is dropped.  Returns False if it had already finished."""
+        request = self._requests[request_id]
+        if request.is_finished:
+            return False
+        self.scheduler.abort(request, reason)
+        return True
+
     def request(self, request_id: str) -> Request:
         return self._requests[request_id]
 

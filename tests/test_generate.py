@@ -255,3 +255,29 @@ def test_stream_yields_tokens_as_they_come(model_folders):
         if n == 5:
             ids.append(engine.add_request(prompts[2], SamplingParams(max_new_tokens=12)))
     assert [got[i] for i in ids] == want and not engine.has_work
+
+
+def test_abort_frees_at_once_and_disturbs_nobody(model_folders):
+    """A request aborted while a step launched ahead still carries it: its pages and slot come back at
+    once, its late token is dropped, the other request's tokens are what they are alone."""
+    from edgerag_b200 import Engine, SamplingParams
+
+    folder = model_folders("b", "float32", std=0.2)
+    cfg = plain.read_config(folder)
+    prompts = [helpers.random_sequence(cfg["vocab"], n, 800 + n) for n in (14, 23)]
+    alone = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=32, max_batch_size=1)
+    want = alone.generate([prompts[1]], SamplingParams(max_new_tokens=20))[0]
+    engine = Engine.from_pretrained(folder, dtype="float32", block_size=8, num_blocks=32, max_batch_size=2,
+                                    max_prefills_per_step=2, poison_freed_pages=True)
+    a = engine.add_request(prompts[0], SamplingParams(max_new_tokens=50))
+    b = engine.add_request(prompts[1], SamplingParams(max_new_tokens=20))
+    for _ in range(6):
+        engine.step()
+    assert engine.lookahead_steps > 0 and engine.abort(a) and not engine.abort(a)
+    held_by_b = sum(engine.cache.held_pages(b))
+    assert engine.cache.free_pages() == [32 - held_by_b] and engine.request(a).finish_reason == "aborted"
+    n_a = len(engine.request(a).generated_token_ids)
+    for ev in engine.stream():
+        assert ev.request_id == b
+    assert engine.request(b).generated_token_ids == want and len(engine.request(a).generated_token_ids) == n_a
+    assert engine.cache.free_pages() == [32] and engine.cache.slots.num_free == 2
