@@ -20,6 +20,9 @@ SIZES = {
     # SmolVLM-256M decoder: 9 query heads on 3 kv heads
     "256m": dict(hidden_size=576, num_attention_heads=9, num_key_value_heads=3, head_dim=64, intermediate_size=1536,
                  vocab_size=49280, rope_theta=100000.0),
+    # SmolVLM-500M decoder: 15 query heads on 5 kv heads (one decode block serves all five)
+    "500m": dict(hidden_size=960, num_attention_heads=15, num_key_value_heads=5, head_dim=64, intermediate_size=2560,
+                 vocab_size=49280, rope_theta=100000.0),
 }
 
 
@@ -31,8 +34,8 @@ def folder_for(tmp, which, dtype):
                                     dtype=getattr(torch, dtype))
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-@pytest.mark.parametrize("which", ["2b", "256m"])
+@pytest.mark.parametrize("which,dtype", [("2b", "bfloat16"), ("2b", "float32"), ("256m", "bfloat16"), ("256m", "float32"),
+                                         ("500m", "bfloat16")])
 def test_cuttings_at_real_layer_sizes(which, dtype, tmp_path):
     folder = folder_for(tmp_path, which, dtype)
     cfg = plain.read_config(folder)
