@@ -8,6 +8,7 @@ Nothing here falls back to PyTorch arithmetic: a missing library or a refused sh
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -100,7 +101,8 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 def _stream() -> int:
     """The raw handle of the current CUDA stream (the capturing stream inside a graph capture)."""
-    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+    # (the C calls directly: torch.cuda.current_device() costs a microsecond of Python per launch)
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 def _need(t: torch.Tensor | None, name: str, dtype=None, contiguous: bool = True) -> None:
@@ -360,6 +362,12 @@ _sm_counts: dict[int, int] = {}
 
 
 def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int, head_dim: int = 64) -> int:
+    """Keys per split for the decode kernels (see ``_choose_decode_split``; answers are remembered)."""
+    return _choose_decode_split(torch._C._cuda_getDevice(), n_seqs, n_kv_heads, max_keys, page_size, head_dim)
+
+
+@functools.lru_cache(maxsize=4096)
+def _choose_decode_split(device: int, n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int, head_dim: int) -> int:
     """Keys per split for the decode kernels, from 128 to 2048.
 
     The bulk kernel runs one block per (sequence, group of neighbouring kv heads, split), two blocks per SM.
@@ -369,7 +377,6 @@ def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: 
     two waves on, the largest such split, but no more than 1024 keys once there are many waves.  A function of the batch's size and of a power-of-two
     bound on its longest context only, so an eager step and a captured one make the same choice.
     """
-    device = torch.cuda.current_device()
     sms = _sm_counts.get(device)
     if sms is None:
         sms = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
@@ -454,6 +461,7 @@ def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
         launch_counts["own"] -= 1       # a single split writes the result itself: no second kernel
 
 
+@functools.lru_cache(maxsize=4096)
 def decode_gqa_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_heads: int, n_kv_heads: int,
                          page_size: int, split_keys: int, max_splits: int = 1) -> bool:
     """Shapes the tensor-core decode kernel for grouped query heads takes: bfloat16, head size 64,
