@@ -17,6 +17,9 @@ of 8192 tokens.  A "step" is one decode step of the whole batch.
   requests) over its time, against the measured copy bandwidth.
 * ``points``: decode throughput at batch 1 and 64 with the same context, and at batch 1, 8 and 64
   with a short context of 640 tokens (``decode_b8_ctx640`` ...), where the weights dominate the bytes.
+* ``spread`` (and ``*_p50_ms`` / ``*_std_ms`` beside every point): every timed step is a trial of its
+  own (an event after each), reported as median, 95th percentile and standard deviation; the prefill
+  is the median of five runs.
 
 The step's inputs (3.4 GB of weights, 12.9 GB of cache at batch 8) are far larger than the 126 MB
 L2, so no flush is needed between timed iterations.  ``--impl reference`` runs the unmodified
@@ -119,6 +122,16 @@ class ClockSampler:
                 "reasons": sorted(self.reasons)}
 
 
+def spread(samples_ms: list[float]) -> dict:
+    """Median, 95th percentile and standard deviation of per-trial times (the reference reports p50,
+    p95 and std over at least five trials and refuses a single number: bench/bench.py:159-227,
+    bench/metrics.py:165-200)."""
+    xs = sorted(samples_ms)
+    p95 = xs[min(len(xs) - 1, int(math.ceil(0.95 * len(xs))) - 1)]
+    return {"trials": len(xs), "p50_ms": round(statistics.median(xs), 4), "p95_ms": round(p95, 4),
+            "std_ms": round(statistics.pstdev(xs), 4) if len(xs) > 1 else 0.0}
+
+
 def model_numbers(cfg: dict, n_layers: int) -> dict:
     h, d = cfg["hidden_size"], cfg["head_dim"]
     nq, nkv, inter, vocab = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"], cfg["vocab_size"]
@@ -165,29 +178,32 @@ def run_ours(args) -> dict:
     gen = torch.Generator().manual_seed(0)
     clocks = ClockSampler()
 
-    def timed_decode(entries_fn, steps: int, warmup: int) -> tuple[float, int]:
-        """K decode steps of the step function plus sampling, on the device clock.  Returns (ms/step, own launches)."""
+    def timed_decode(entries_fn, steps: int, warmup: int) -> tuple[float, int, dict]:
+        """K decode steps of the step function plus sampling, on the device clock.  An event after every
+        step makes each step a trial of its own.  Returns (ms/step over the whole region, own launches,
+        spread of the K per-step times)."""
         tokens = torch.empty(256, dtype=torch.int32, device="cuda")
         for _ in range(warmup):
             kernels.sample_rows(runner.step(entries_fn()), tokens)
         torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         before = kernels.launch_counts["own"]
         sampler = ClockSampler()
         with sampler:
-            start.record()
-            for _ in range(steps):
+            marks[0].record()
+            for i in range(steps):
                 kernels.sample_rows(runner.step(entries_fn()), tokens)
-            stop.record()
+                marks[i + 1].record()
             torch.cuda.synchronize()
         clocks.merge(sampler)
-        return start.elapsed_time(stop) / steps, kernels.launch_counts["own"] - before
+        per_step = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+        return marks[0].elapsed_time(marks[steps]) / steps, kernels.launch_counts["own"] - before, spread(per_step)
 
     # --- prefill: one step with 2,048 prompt tokens -------------------------------------------------
     prefill_tokens = 2048
     ids = torch.randint(0, vocab, (prefill_tokens,), generator=gen).tolist()
     times = []
-    for i in range(4):
+    for i in range(7):
         runner.admit(f"p{i}")
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -197,12 +213,14 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b))
         runner.release(f"p{i}")
-    prefill_ms = min(times[1:])
+    prefill_spread = spread(times[2:])          # five trials after two warm-up runs
+    prefill_ms = prefill_spread["p50_ms"]
     pairs = prefill_tokens * (prefill_tokens + 1) / 2
     prefill_flops = 2.0 * prefill_tokens * nums["linear_params"] + 2.0 * nums["head_params"] + nums["attn_flops_per_pair"] * pairs
     prefill = {"value": round(prefill_tokens / (prefill_ms / 1e3), 1), "tokens": prefill_tokens, "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
-               "tflop": round(prefill_flops / 1e12, 3)}
+               "tflop": round(prefill_flops / 1e12, 3), "ms_min": round(min(times[2:]), 3),
+               "std_ms": prefill_spread["std_ms"], "trials": prefill_spread["trials"]}
 
     # --- the headline: batch 8 at the full context, through the entry point --------------------------
     k, w = args.steps, args.warmup
@@ -217,24 +235,30 @@ def run_ours(args) -> dict:
     torch.cuda.synchronize()
     sampler = ClockSampler()
     h2d = d2h = 0
+    e2e_steps = []
     with sampler:
-        t0 = time.perf_counter()
+        t0 = last = time.perf_counter()
         for _ in range(k):
             events = engine.step()
             h2d += runner.h2d_bytes_last
             d2h += engine.d2h_bytes_last
+            now = time.perf_counter()
+            e2e_steps.append(1e3 * (now - last))
+            last = now
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
     clocks.merge(sampler)
     if len(events) != batch:
         raise RuntimeError(f"{len(events)} of {batch} requests were decoding in the timed steps")
     e2e = {"value": round(batch * k / e2e_s, 1), "unit": "tokens/s", "ms_per_step": round(1e3 * e2e_s / k, 4),
-           "h2d_bytes_per_step": h2d // k, "d2h_bytes_per_step": d2h // k}
+           "h2d_bytes_per_step": h2d // k, "d2h_bytes_per_step": d2h // k,
+           **{f"step_{key}": v for key, v in spread(e2e_steps).items() if key != "trials"}}
 
     # the same requests, driven below the scheduler with fixed ids, on the device clock
     live = [f"d{i}" for i in range(batch)]
     fixed = torch.randint(0, vocab, (batch,), generator=gen).tolist()
-    ms_per_step, launches = timed_decode(lambda: [StepEntry(r, tokens=[t], want=[0]) for r, t in zip(live, fixed)], k, w)
+    ms_per_step, launches, step_spread = timed_decode(
+        lambda: [StepEntry(r, tokens=[t], want=[0]) for r, t in zip(live, fixed)], k, w)
     ctx_lens = [cache.requests[r].num_tokens for r in live]
     need = decode_bytes(nums, ctx_lens)
     achieved = need / (ms_per_step / 1e3) / 1e9
@@ -257,10 +281,11 @@ def run_ours(args) -> dict:
             cache.advance(r, ctx - 2 * (k + w) - 4)
         # pages keep what earlier requests wrote: finite bfloat16 values either way
         toks = torch.randint(0, vocab, (pb,), generator=gen).tolist()
-        ms, _ = timed_decode(lambda: [StepEntry(r, tokens=[t], want=[0]) for r, t in zip(names, toks)], k, w)
+        ms, _, sp = timed_decode(lambda: [StepEntry(r, tokens=[t], want=[0]) for r, t in zip(names, toks)], k, w)
         tag = f"decode_b{pb}" if ctx == context else f"decode_b{pb}_ctx{ctx}"
         points[tag] = round(pb / (ms / 1e3), 1)
         points[f"{tag}_ms"] = round(ms, 4)
+        points[f"{tag}_p50_ms"], points[f"{tag}_std_ms"] = sp["p50_ms"], sp["std_ms"]
         lens = [cache.requests[r].num_tokens for r in names]
         points[f"{tag}_hbm_frac"] = round(decode_bytes(nums, lens) / (ms / 1e3) / 1e9 / peak["hbm_gbs"], 4)
         for r in names:
@@ -280,7 +305,7 @@ def run_ours(args) -> dict:
             "peaks": peak_source, "cuda_graphs": bool(engine.options.cuda_graphs and runner.graphs_enabled),
         },
         "clocks": clocks.record(), "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill,
-        "roofline": roofline, "points": points,
+        "roofline": roofline, "points": points, "spread": step_spread,
     }
 
 

@@ -2,7 +2,9 @@
 
 One allocation per cache group, made once (the reference's arena: edgerag/serve/executor.py:76-83),
 laid out ``[layer, k|v, page, kv head, offset, head_dim]`` so that one (layer, page, head) is a
-contiguous ``page_size * head_dim`` run: the unit an attention kernel streams.
+contiguous ``page_size * head_dim`` run: the unit an attention kernel streams.  A group whose
+values have another width than its keys (``KVGroupSpec.v_head_dim``) gets a key pool and a value
+pool of their own, each ``[layer, page, kv head, offset, width]``.
 """
 
 from __future__ import annotations
@@ -22,24 +24,36 @@ class DevicePools:
         self.dtype = dtype
         self.device = device
         self.poison = poison
-        self.kv: list[torch.Tensor] = []
+        #: per group: (key pool, value pool, the dimension of each that counts pages)
+        self._pools: list[tuple[torch.Tensor, torch.Tensor, int]] = []
+        self.kv: list[torch.Tensor] = []         # the allocations themselves (one or two per group)
+        fill = float("nan") if poison else 0.0
         for g, n in zip(layout.groups, num_pages):
-            shape = (g.n_layers, 2, n, g.n_kv_heads, page_size, g.head_dim)
-            pool = torch.empty(shape, dtype=dtype, device=device)
-            pool.fill_(float("nan") if poison else 0.0)
-            self.kv.append(pool)
+            if g.value_dim == g.head_dim:
+                pool = torch.empty((g.n_layers, 2, n, g.n_kv_heads, page_size, g.head_dim), dtype=dtype, device=device)
+                pool.fill_(fill)
+                self.kv.append(pool)
+                self._pools.append((pool[:, 0], pool[:, 1], 1))
+            else:
+                keys = torch.empty((g.n_layers, n, g.n_kv_heads, page_size, g.head_dim), dtype=dtype, device=device)
+                values = torch.empty((g.n_layers, n, g.n_kv_heads, page_size, g.value_dim), dtype=dtype, device=device)
+                keys.fill_(fill), values.fill_(fill)
+                self.kv += [keys, values]
+                self._pools.append((keys, values, 1))
         self.states: dict[str, torch.Tensor] = {
             s.name: torch.zeros((max_requests, *s.shape), dtype=_STATE_DTYPES[s.dtype], device=device)
             for s in layout.states
         }
 
     def pages_of(self, cache_layer: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """Key pages and value pages ``[pages, kv heads, page_size, head_dim]`` of one cache layer."""
+        """Key pages ``[pages, kv heads, page_size, head_dim]`` and value pages (the same shape, or
+        ``v_head_dim`` wide where the group says so) of one cache layer."""
         placed = self.layout.placement[cache_layer]
         if placed is None:
             raise KeyError(f"cache layer {cache_layer} holds no pages")
         group, local = placed
-        return self.kv[group][local, 0], self.kv[group][local, 1]
+        keys, values, _ = self._pools[group]
+        return keys[local], values[local]
 
     def zero_slots(self, slots: list[int]) -> None:
         if slots and self.states:
@@ -51,11 +65,12 @@ class DevicePools:
         """Overwrite freed pages with NaN (tests: a read of a stale page then shows in the logits)."""
         if not (self.poison and freed):
             return
-        for g in range(len(self.kv)):
+        for g, (keys, values, page_dim) in enumerate(self._pools):
             pages = [p for gi, p in freed if gi == g]
             if pages:
                 index = torch.tensor(pages, dtype=torch.long, device=self.device)
-                self.kv[g].index_fill_(2, index, float("nan"))
+                keys.index_fill_(page_dim, index, float("nan"))
+                values.index_fill_(page_dim, index, float("nan"))
 
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv) + sum(

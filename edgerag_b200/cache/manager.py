@@ -40,10 +40,17 @@ class KVGroupSpec:
     n_kv_heads: int
     head_dim: int
     window: int = 0  # 0: every earlier key stays visible
+    #: width of a cached value row when it differs from the key's (a mixer that caches keys and
+    #: values of different sizes, or a single latent per token with ``v_head_dim = 0``); None: head_dim
+    v_head_dim: int | None = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
     def page_elements(self, page_size: int) -> int:
         """Elements one page holds over all layers of the group (keys and values)."""
-        return 2 * self.n_layers * self.n_kv_heads * page_size * self.head_dim
+        return self.n_layers * self.n_kv_heads * page_size * (self.head_dim + self.value_dim)
 
 
 @dataclass(frozen=True)

@@ -9,7 +9,9 @@ Keys read (from ``text_config`` when the file is a SmolVLM composite, else from 
 ``num_hidden_layers, hidden_size, num_attention_heads, num_key_value_heads, head_dim, vocab_size,
 max_position_embeddings, rope_parameters.rope_theta | rope_theta, pad_token_id, rms_norm_eps,
 intermediate_size, hidden_act, tie_word_embeddings``; from the top level ``architectures`` and
-``model_type``.
+``model_type``.  Keys that would change the arithmetic and are not implemented are refused by name:
+``rope_scaling`` / ``rope_parameters.rope_type`` other than default, ``partial_rotary_factor``,
+``attention_bias``, ``mlp_bias``, ``sliding_window``, logit soft-capping.
 """
 
 from __future__ import annotations
@@ -34,6 +36,40 @@ def _rope_theta(txt: dict[str, Any], where: str) -> float:
     raise ConfigError(
         f"{where}: rope_theta is neither in rope_parameters nor a key of its own; refusing to default it"
     )
+
+
+def _refuse_what_is_not_built(txt: dict[str, Any], where: str) -> None:
+    """Options of Llama-style configurations that change the arithmetic and that this decoder does not
+    implement (the reference has none of them either: edgerag/core/layers.py:63-90 has one rotary
+    formula, edgerag/core/layers.py:280-283,336-338 build every projection without bias, and
+    edgerag/core/layers.py:243-254 masks causally without a window).  A model that sets one of them
+    would load and run with wrong logits, so it is refused by the key's name."""
+    scaling = txt.get("rope_scaling")
+    if scaling is not None:
+        kind = scaling.get("rope_type", scaling.get("type")) if isinstance(scaling, dict) else scaling
+        if kind not in (None, "default"):
+            raise ConfigError(f"{where}: rope_scaling of type {kind!r} is not supported (plain rotary angles only)")
+    params = txt.get("rope_parameters")
+    if isinstance(params, dict):
+        kind = params.get("rope_type", params.get("type"))
+        if kind not in (None, "default"):
+            raise ConfigError(f"{where}: rope_parameters.rope_type {kind!r} is not supported (plain rotary angles only)")
+        factor = params.get("factor")
+        if factor not in (None, 1, 1.0):
+            raise ConfigError(f"{where}: rope_parameters.factor {factor!r} is not supported")
+        partial = params.get("partial_rotary_factor")
+        if partial not in (None, 1, 1.0):
+            raise ConfigError(f"{where}: rope_parameters.partial_rotary_factor {partial!r} is not supported")
+    if txt.get("partial_rotary_factor") not in (None, 1, 1.0):
+        raise ConfigError(f"{where}: partial_rotary_factor {txt['partial_rotary_factor']!r} is not supported")
+    for key in ("attention_bias", "mlp_bias"):
+        if txt.get(key):
+            raise ConfigError(f"{where}: {key} is set; projections with a bias are not supported")
+    if txt.get("use_sliding_window") or (txt.get("sliding_window") and txt.get("use_sliding_window") is not False):
+        raise ConfigError(f"{where}: sliding_window is set; this architecture attends to every earlier token")
+    for key in ("attn_logit_softcapping", "final_logit_softcapping"):
+        if txt.get(key):
+            raise ConfigError(f"{where}: {key} is set; logit soft-capping is not supported")
 
 
 def _need(txt: dict[str, Any], key: str, where: str) -> Any:
@@ -114,6 +150,7 @@ class DecoderConfig:
         architecture = archs[0] if archs else raw.get("model_type")
         if not architecture:
             raise ConfigError(f"{where}: neither 'architectures' nor 'model_type' names the model")
+        _refuse_what_is_not_built(txt, where)
         heads = int(_need(txt, "num_attention_heads", where))
         hidden = int(_need(txt, "hidden_size", where))
         tie = txt.get("tie_word_embeddings", raw.get("tie_word_embeddings", False))

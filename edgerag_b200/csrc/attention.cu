@@ -248,7 +248,9 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_a
   const int t = token_of_seq[seq];
   const int pos = positions[t];
   const int k_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int n_splits = pos / split_keys - k_lo / split_keys + 1;
+  // never beyond what the split kernel's grid wrote (a caller that understates max_splits gets the
+  // first max_splits splits merged, not its neighbours' scratch)
+  const int n_splits = min(pos / split_keys - k_lo / split_keys + 1, max_splits);
   const size_t base = ((size_t)seq * nq + h) * max_splits;
   float m = -INFINITY;
   for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);

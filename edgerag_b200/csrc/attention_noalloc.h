@@ -11,10 +11,17 @@
 // `erb_attention_decode_static` is `erb_attention_decode` with that scratch taken from a
 // fixed array inside the library instead of from the caller:
 //
-//   * The array is `ERB_STATIC_SCRATCH_FLOATS` floats (4 MiB).  Every GPU that loads the library
-//     holds that much until the process exits, whether or not the function is ever called.
+//   * The array is `ERB_STATIC_SCRATCH_FLOATS` floats (4 MiB).  Every GPU on which the library's
+//     device code is loaded holds that much until the process exits.  The CUDA runtime may load
+//     that code lazily, at the first call into the library on a device, and this load is the one
+//     moment at which the array's 4 MiB are taken: on a GPU that is already full it fails with an
+//     out-of-memory error.  So make one call on each device at start-up, before the memory is
+//     given away.
 //   * A call needs n_seqs * nq * max_splits * (head_dim + 2) floats.  A call that needs more is
-//     refused with ERB_ERR_UNSUPPORTED and a message; nothing is launched.
+//     refused with ERB_ERR_UNSUPPORTED and a message; nothing is launched.  `max_splits` must be
+//     at least the number of splits of the longest sequence; with a smaller value only the first
+//     `max_splits` splits of a sequence are computed and merged (the result is then wrong, but no
+//     kernel reads or writes outside the part of the array that the call was sized for).
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
 //     with that device current) and remembers it.  Make that first call outside of any stream
 //     capture.  Later calls only launch kernels.

@@ -729,7 +729,7 @@ attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const f
   __shared__ float s_red[2];
   const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
   const int t = token_of_seq[seq];
-  const int n_splits = positions[t] / split_keys + 1;
+  const int n_splits = min(positions[t] / split_keys + 1, max_splits);   // never beyond what the split kernel wrote
   const size_t base = ((size_t)seq * nq + h) * max_splits;
   float m_i = -INFINITY, l_i = 0.f;
   if (tid < n_splits) { m_i = part_ml[(base + tid) * 2]; l_i = part_ml[(base + tid) * 2 + 1]; }

@@ -358,7 +358,7 @@ ERB_EXPORT int erb_rope_cache_write(void* qkv, const int* positions, const float
       !((uintptr_t)v_pages & 15)) {
     const int items = (nq + nkv) * head_dim / 8 + nkv * head_dim / 4;
     int y = (items + 127) / 128;
-    const int want = (148 * 8 + n_tokens - 1) / n_tokens;      // enough blocks for every SM
+    const int want = (sm_count() * 8 + n_tokens - 1) / n_tokens;      // enough blocks for every SM
     if (y > want) y = want;
     if (y < 1) y = 1;
     launch_chained(rope_cache_write_vec4_kernel<elem_t>, dim3(dim3(n_tokens, y)), dim3(128), head_dim * sizeof(float), (cudaStream_t)stream, 

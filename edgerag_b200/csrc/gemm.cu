@@ -309,14 +309,15 @@ template <int NT, int MODE>
 int launch_skinny_mode(const __nv_bfloat16* ap, const __nv_bfloat16* wp, void* out, int M, int N, int K, int lda,
                        int ldw, int ldo, cudaStream_t s, RopeArgs ra = RopeArgs{}) {
   const unsigned blocks = (unsigned)(MODE == 2 ? (N + 7) / 8 : (N + 15) / 16);
+  const unsigned sms = (unsigned)sm_count();
   if constexpr (NT <= 2) {
-    if (blocks <= 148 && K >= 4096) {           // at most one block per SM and long rows: 32 warps per block
+    if (blocks <= sms && K >= 4096) {           // at most one block per SM and long rows: 32 warps per block
       launch_chained(linear_skinny_kernel<NT, MODE, 32>, dim3(blocks), dim3(1024), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo, ra);
       return check_launch("linear_skinny");
     }
   }
   if constexpr (NT <= 2) {
-    if (blocks < 2 * 148 && K >= 1024) {        // few blocks: twice the warps per block
+    if (blocks < 2 * sms && K >= 1024) {        // few blocks: twice the warps per block
       launch_chained(linear_skinny_kernel<NT, MODE, 16>, dim3(blocks), dim3(512), 0, s, ap, wp, out, M, N, K, lda, ldw, ldo, ra);
       return check_launch("linear_skinny");
     }

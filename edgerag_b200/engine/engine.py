@@ -30,7 +30,6 @@ from ..sampling.sampler import PendingTokens, Sampler
 from ..weights.loader import load_safetensors, random_tensors
 from .request import Request, RequestState
 from .scheduler import Batch, ScheduledEntry, Scheduler, SchedulerConfig
-from ..cache.allocator import OutOfPagesError
 from .step import ModelRunner, StepEntry
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -256,13 +255,14 @@ class Engine:
             self.runner.feedback = self.sampler.device_tokens
         try:
             logits = self.runner.step(self._entries(batch, fed_rows))
+        except OutOfPagesError:
+            if after is None:
+                self._fail(batch, "OutOfPagesError")
+            raise       # launched ahead: nothing was changed, the scheduler decides after the step before
         except Exception as exc:
-            if after is not None:
-                raise
             # Every request of the batch fails and frees its pages; the engine stays usable
             # (edgerag/serve/engine.py:178-189).
-            for e in batch.entries:
-                self.scheduler.abort(e.request, f"error: {type(exc).__name__}")
+            self._fail(batch, type(exc).__name__)
             raise
         sampled = [e for e in batch.entries if e.samples]
         pending = None
@@ -272,6 +272,13 @@ class Engine:
                 logits, [e.request.sampling for e in sampled], [e.request.seed for e in sampled],
                 [e.request.num_generated + ahead for e in sampled])
         return _Launched(batch, sampled, pending)
+
+    def _fail(self, batch: Batch, why: str) -> None:
+        """A step of this batch raised, or its results are not valid: its requests end with
+        ``finish_reason`` "error: ..." and give back their pages and slots."""
+        for e in batch.entries:
+            if not e.request.is_finished:
+                self.scheduler.abort(e.request, f"error: {why}")
 
     def _following(self, cur: "_Launched") -> Batch | None:
         """The batch that follows ``cur`` if nothing unforeseen happens in it, or None when the next
@@ -296,13 +303,20 @@ class Engine:
     def _collect(self, done: "_Launched") -> list[TokenEvent]:
         """Read a launched step's tokens and commit it.  Entries of requests that finished meanwhile
         (a stop token in the step before) are dropped."""
-        live = [e for e in done.sampled if not e.request.is_finished]
         new_tokens: dict[str, int] = {}
         if done.pending is not None:
             tokens = done.pending.read()
             new_tokens = {e.request.request_id: t for e, t in zip(done.sampled, tokens)}
-            self.runner.raise_if_flagged()       # reading synchronised: the status copy is current
+            try:
+                self.runner.raise_if_flagged()       # reading synchronised: the status copy is current
+            except Exception as exc:
+                # A kernel of this step (or of one launched after it) gave up: nothing of it is kept.
+                # A step launched ahead holds the same requests; it is dropped with them.
+                self._fail(done.batch, type(exc).__name__)
+                self._in_flight = None
+                raise
             self.d2h_bytes_last = 4 * len(tokens)
+        live = [e for e in done.sampled if not e.request.is_finished]
         self.scheduler.update(done.batch, new_tokens)
         events = []
         for e in live:
@@ -321,6 +335,7 @@ class Engine:
             if batch.is_empty:
                 return []
             cur = self._launch(batch)
+        failure = None
         if self.options.lookahead:
             follow = self._following(cur)
             if follow is not None:
@@ -329,7 +344,15 @@ class Engine:
                     self.lookahead_steps += 1
                 except OutOfPagesError:
                     pass        # nothing was changed; the scheduler decides after this step
-        return self._collect(cur)
+                except Exception as exc:
+                    # The step launched ahead failed and took its requests with it (``_launch``).  The
+                    # step before it is still collected, so that the scheduler's books and the cache
+                    # agree for every request that goes on; then the failure is reported.
+                    failure = exc
+        events = self._collect(cur)
+        if failure is not None:
+            raise failure
+        return events
 
     def stream(self) -> "Iterator[TokenEvent]":
         """Run steps while there is work and yield every generated token as soon as the host has it

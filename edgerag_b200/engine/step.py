@@ -348,6 +348,9 @@ class ModelRunner:
         the status word, so callers that synchronise anyway pay nothing extra)."""
         code = int(self._status_host[0])
         if code:
+            # Steps that are still on the device (one launched ahead) would copy the same code to the
+            # host once more after it has been cleared here: let them finish first.
+            torch.cuda.current_stream().synchronize()
             self.status.zero_()
             self._status_host.zero_()
             if code >= 1000000:

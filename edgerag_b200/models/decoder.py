@@ -61,14 +61,14 @@ class DecoderModel:
                     raise ValueError(f"cache layer {call.cache_layer} is written by two calls of the run order")
                 owner[call.cache_layer] = call.layer
         layout = CacheLayout(placement=[None] * n_cache_layers)
-        keys: list[tuple[int, int, int]] = []
+        keys: list[tuple[int, int, int, int | None]] = []
         counts: list[int] = []
         for cl, layer in enumerate(owner):
             if layer is None:
                 raise ValueError(f"cache layer {cl} is read but never written")
             spec = self.blocks[layer].mixer.cache_spec()
             if isinstance(spec, KVGroupSpec):
-                key = (spec.n_kv_heads, spec.head_dim, spec.window)
+                key = (spec.n_kv_heads, spec.head_dim, spec.window, spec.v_head_dim)
                 if key not in keys:
                     keys.append(key)
                     counts.append(0)

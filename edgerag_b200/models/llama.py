@@ -35,6 +35,8 @@ def llama_plan(cfg: DecoderConfig) -> ModelPlan:
         layers=layers,
         schedule=[LayerCall(i, i) for i in range(cfg.n_layers)],
         final_norm=norm("norm."),
-        head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": h, "tied": cfg.tie_word_embeddings}, "lm_head."),
+        # a tied head shares the embedding table when the checkpoint stores no lm_head.weight
+        head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": h,
+                                 "tied_to": "embed_tokens.weight" if cfg.tie_word_embeddings else None}, "lm_head."),
         ignored_prefixes=("model.vision_model.", "model.connector.", "vision_model.", "connector."),
     )

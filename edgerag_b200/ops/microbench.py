@@ -7,8 +7,10 @@
 
 Each case builds random inputs larger than the 126 MB L2 where the real workload is (or says that
 it is not), runs warm-up launches, then times ``--iters`` launches replayed from one CUDA graph with
-CUDA events and prints one JSON line with the median per launch.  The same commands, under ``ncu``, produce the summaries in
-``profiles/``.
+CUDA events and prints one JSON line with the median per launch.  Fractions are of the peaks in a
+JSON file ``{"hbm_gbs": ..., "bf16_tflops": ...}`` named by ``--peaks`` or, by default,
+``MEASURED_PEAKS.json`` in the working directory or beside the package; without such a file they
+are of the stated defaults, and the line says which (``"peaks"``).
 """
 
 from __future__ import annotations
@@ -17,12 +19,30 @@ import argparse
 import json
 import statistics
 import sys
+from pathlib import Path
 
 import torch
 
 from . import kernels
 
-HBM_GBS, BF16_TFLOPS = 6650.0, 1590.0   # the pool's earlier measurement, used when no measured file is given
+HBM_GBS, BF16_TFLOPS = 6650.0, 1590.0   # defaults (a B200's copy bandwidth and library bf16 product rate) when no file is found
+PEAKS_FROM = "defaults"
+
+
+def load_peaks(path: str | None) -> None:
+    """Take the roofline denominators from a JSON file of measured peaks, if there is one."""
+    global HBM_GBS, BF16_TFLOPS, PEAKS_FROM
+    candidates = [Path(path)] if path else [Path.cwd() / "MEASURED_PEAKS.json",
+                                            Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"]
+    for cand in candidates:
+        try:
+            raw = json.loads(cand.read_text())
+            HBM_GBS, BF16_TFLOPS, PEAKS_FROM = float(raw["hbm_gbs"]), float(raw["bf16_tflops"]), f"measured ({cand.name})"
+            return
+        except (OSError, KeyError, ValueError):
+            continue
+    if path:
+        raise SystemExit(f"--peaks {path}: not a JSON file with hbm_gbs and bf16_tflops")
 
 
 def _time(fn, iters: int, warmup: int, rounds: int = 5) -> float:
@@ -198,6 +218,7 @@ def main(argv=None) -> int:
     common.add_argument("--iters", type=int, default=20)
     common.add_argument("--warmup", type=int, default=3)
     common.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    common.add_argument("--peaks", default=None, help="JSON file with hbm_gbs and bf16_tflops to take fractions of")
     att = argparse.ArgumentParser(add_help=False)
     att.add_argument("--heads", type=int, default=32)
     att.add_argument("--kv-heads", type=int, default=32)
@@ -232,7 +253,10 @@ def main(argv=None) -> int:
         return 1
     fn = {"decode-attention": decode_attention, "prefill-attention": prefill_attention, "linear": linear,
           "step-kernels": step_kernels}[a.case]
-    print(json.dumps(fn(a)))
+    load_peaks(a.peaks)
+    result = fn(a)
+    result["peaks"] = PEAKS_FROM
+    print(json.dumps(result))
     return 0
 
 

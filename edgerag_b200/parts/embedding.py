@@ -3,8 +3,8 @@
 ``TokenEmbedding``: a plain table lookup without scale, or rows of caller-given embeddings
 (edgerag/core/model.py:106-110: exactly one of ids and embeddings per token); the result is
 written to the float32 residual stream.  ``LMHead``: bias-free projection to float32 logits over
-the rows that were asked for (edgerag/core/model.py:150-152); a checkpoint without
-``lm_head.weight`` whose config ties the embeddings shares the table.
+the rows that were asked for (edgerag/core/model.py:150-152); where the plan names a tensor to
+tie the head to, a checkpoint without a head of its own shares that tensor.
 """
 
 from __future__ import annotations
@@ -39,14 +39,16 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     graph_safe = True
 
-    def __init__(self, vocab: int, hidden: int, tied: bool, dtype: torch.dtype, device: torch.device) -> None:
-        self.vocab, self.hidden, self.tied = vocab, hidden, tied
+    def __init__(self, vocab: int, hidden: int, dtype: torch.dtype, device: torch.device,
+                 tied_to: str | None = None) -> None:
+        """``tied_to``: model-relative name of the tensor to share when the checkpoint has no head of
+        its own (the plan names it; this part does not know what the model calls its embedding)."""
+        self.vocab, self.hidden, self.tied_to = vocab, hidden, tied_to
         self.dtype, self.device = dtype, device
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec("weight", (self.vocab, self.hidden),
-                           fallback="embed_tokens.weight" if self.tied else None)]
+        return [WeightSpec("weight", (self.vocab, self.hidden), fallback=self.tied_to)]
 
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].to(device=self.device, dtype=self.dtype).contiguous()

@@ -3,7 +3,8 @@
 The reference copies tensors attribute by attribute out of a loaded library module
 (edgerag/core/model.py:274-295) and reports a wrong shape per tensor (edgerag/core/linear.py:85-98).
 Here the model lists the tensors it needs (``WeightSpec``: name, shape, kind), the loader finds
-each under the prefixes a checkpoint may carry, and **one** error reports every missing tensor,
+each under the prefixes a checkpoint may carry (in ``model.safetensors``, or in the shards that
+``model.safetensors.index.json`` names), and **one** error reports every missing tensor,
 every unexpected tensor and every wrong shape together.
 
 Element types follow the spec's kind: matrices are cast to the engine's element type (bfloat16
@@ -29,10 +30,11 @@ class WeightsError(ValueError):
     """The checkpoint does not fit the model.  The message lists every offender."""
 
     def __init__(self, where: str, missing: list[str], unexpected: list[str],
-                 wrong_shape: list[tuple[str, tuple, tuple]], wrong_type: list[tuple[str, str]] = ()) -> None:
+                 wrong_shape: list[tuple[str, tuple, tuple]], wrong_type: list[tuple[str, str]] = (),
+                 note: str = "") -> None:
         self.missing, self.unexpected = list(missing), list(unexpected)
         self.wrong_shape, self.wrong_type = list(wrong_shape), list(wrong_type)
-        lines = [f"{where}: the checkpoint does not fit the model"]
+        lines = [f"{where}: the checkpoint does not fit the model" + (f" ({note})" if note else "")]
         if self.missing:
             lines.append(f"  missing tensors ({len(self.missing)}): " + ", ".join(self.missing))
         if self.unexpected:
@@ -56,15 +58,82 @@ def _target_dtype(kind: str, stored: torch.dtype, compute: torch.dtype) -> torch
     return compute
 
 
+class _Checkpoint:
+    """The tensors of a model folder by name: ``model.safetensors``, or the shards that
+    ``model.safetensors.index.json`` lists (``{"weight_map": {tensor name: shard file}}``), which is
+    how checkpoints too large for one file are stored."""
+
+    def __init__(self, folder: Path) -> None:
+        self.where = str(folder / "model.safetensors")
+        self.files: list[SafetensorsFile] = []
+        self.file_of: dict[str, SafetensorsFile] = {}
+        single, index = folder / "model.safetensors", folder / "model.safetensors.index.json"
+        try:
+            if single.is_file() or not index.is_file():
+                self._open(single)            # (a missing file raises the container's own error)
+                return
+            self.where = str(index)
+            try:
+                weight_map = json.loads(index.read_text())["weight_map"]
+                assert isinstance(weight_map, dict) and weight_map
+            except (json.JSONDecodeError, KeyError, AssertionError, UnicodeDecodeError) as exc:
+                raise WeightsError(self.where, [], [], [], note=f"not a shard index with a weight_map ({exc!r})") from exc
+            lost = sorted({str(f) for f in weight_map.values() if not (folder / str(f)).is_file()})
+            if lost:
+                raise WeightsError(self.where, [], [], [], note="shard files that the index names are absent: " + ", ".join(lost))
+            opened = {shard: self._open(folder / shard) for shard in sorted({str(f) for f in weight_map.values()})}
+            # the index decides where a name is read from; a tensor it names must be in that shard
+            stray = sorted(n for n, shard in weight_map.items() if n not in opened[str(shard)].entries)
+            if stray:
+                raise WeightsError(self.where, stray, [], [], note="the index names tensors that their shard does not hold")
+            self.file_of = {n: opened[str(shard)] for n, shard in weight_map.items()}
+            for f in opened.values():          # tensors a shard holds beyond the index are reported as unexpected
+                for n in f.names():
+                    self.file_of.setdefault(n, f)
+        except Exception:
+            self.close()
+            raise
+
+    def _open(self, path: Path) -> SafetensorsFile:
+        f = SafetensorsFile(path)
+        self.files.append(f)
+        for n in f.names():
+            self.file_of.setdefault(n, f)
+        return f
+
+    def names(self) -> set[str]:
+        return set(self.file_of)
+
+    def shape(self, name: str) -> tuple[int, ...]:
+        return self.file_of[name].shape(name)
+
+    def dtype(self, name: str) -> torch.dtype:
+        return self.file_of[name].dtype(name)
+
+    def tensor(self, name: str) -> torch.Tensor:
+        return self.file_of[name].tensor(name)
+
+    def close(self) -> None:
+        for f in self.files:
+            f.close()
+
+    def __enter__(self) -> "_Checkpoint":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+
 def load_safetensors(folder: str | Path, specs: Iterable[WeightSpec], compute_dtype: torch.dtype,
                      device: torch.device, name_prefixes: tuple[str, ...] = ("model.text_model.", "model.", ""),
                      ignored_prefixes: tuple[str, ...] = ()) -> dict[str, torch.Tensor]:
-    """``{model-relative name: tensor on device}`` for every spec, from ``folder/model.safetensors``."""
-    path = Path(folder) / "model.safetensors"
+    """``{model-relative name: tensor on device}`` for every spec, from ``folder/model.safetensors`` or
+    from the shards listed in ``folder/model.safetensors.index.json``."""
     specs = list(specs)
-    with SafetensorsFile(path) as f, warnings.catch_warnings():
+    with _Checkpoint(Path(folder)) as f, warnings.catch_warnings():
         warnings.filterwarnings("ignore", message=".*non-writable.*")
-        stored = set(f.names())
+        path = f.where
+        stored = f.names()
         found: dict[str, str] = {}
         for s in specs:
             for prefix in name_prefixes:

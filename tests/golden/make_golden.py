@@ -9,7 +9,9 @@ random weights (in a temporary directory), loads the same tensors into the refer
 ``EdgeRagDecoder(spec, use_eager=True)`` (edgerag/core/model.py:31-152, built in fp32 from
 ``FP16Linear``, which despite its name is a plain ``nn.Linear`` wrapper, edgerag/core/linear.py:70-104),
 runs whole prompts through it, and stores a subset of the logits rows, the greedy continuation
-produced with the reference's own paged cache (edgerag/cache/paged.py), and the prompts.  It also
+produced with the reference's own paged cache (edgerag/cache/paged.py), the prompts, and the greedy
+tokens of all prompts served together by the reference's own scheduler and executor with prompt
+portions of 4, 8 and 64 tokens (``served_chunk<c>_<i>``).  It also
 prints the largest difference between the reference and ``plain_llama.forward`` on those prompts.
 
 The committed ``golden_tiny_*.safetensors`` files were made by this script; ``tests/test_plain.py``
@@ -36,6 +38,7 @@ CASES = {
     "b": dict(raw=plain.TINY_B, seed=1, std=0.08, prompt_lens=(5, 40, 77), n_new=8),
 }
 ROWS = 12  # logits rows kept per prompt (the last ones)
+CHUNKS = (4, 8, 64)  # prompt portions of the reference's executor (tests/test_executor.py:120-160)
 
 
 def prompts_for(case: dict, vocab: int) -> list[list[int]]:
@@ -83,6 +86,41 @@ def reference_greedy(spec, model, prompt: list[int], n_new: int, block_size: int
     return out
 
 
+@torch.inference_mode()
+def reference_scheduled(spec, model, prompts: list[list[int]], n_new: int, block_size: int, chunk: int) -> list[list[int]]:
+    """Greedy tokens of all prompts served together by the reference's own ``Scheduler`` and
+    ``ModelExecutor`` (edgerag/sched/scheduler.py:95-309, edgerag/serve/executor.py:57-165) with prompt
+    portions of ``chunk`` tokens, driven by the threadless loop of its tests
+    (tests/test_executor.py:54-70): schedule, execute, report portions and tokens, end the step."""
+    from edgerag.cache.allocator import BlockAllocator
+    from edgerag.sched.request import Request
+    from edgerag.sched.scheduler import Scheduler, SchedulerConfig
+    from edgerag.serve.executor import ModelExecutor
+
+    allocator = BlockAllocator(256, block_size)
+    executor = ModelExecutor(model, spec, allocator, torch.device("cpu"), torch.float32, chunk_size=chunk)
+    scheduler = Scheduler(allocator, SchedulerConfig(max_batch_size=len(prompts), prefill_chunk_size=chunk,
+                                                     cow_reserve_blocks=0, max_prefills_per_step=1))
+    requests = [Request(request_id=f"g{i}", prompt_token_ids=list(p), max_new_tokens=n_new) for i, p in enumerate(prompts)]
+    for r in requests:
+        scheduler.add_request(r)
+    for _ in range(10000):
+        if not scheduler.has_work:
+            break
+        batch = scheduler.schedule()
+        out = executor.execute(batch)
+        for r in batch.requests:
+            n = out.prefilled.get(r.request_id, 0)
+            if n:
+                scheduler.on_prefill_chunk(r, n)
+            t = out.tokens.get(r.request_id)
+            if t is not None:
+                scheduler.on_token(r, t)
+        scheduler.end_step()
+    assert all(len(r.generated_token_ids) == n_new for r in requests), [len(r.generated_token_ids) for r in requests]
+    return [list(r.generated_token_ids) for r in requests]
+
+
 def main() -> None:
     from safetensors.torch import save_file
 
@@ -109,6 +147,11 @@ def main() -> None:
                 reference_greedy(spec, model, prompt, case["n_new"], block_size=8 if tag == "b" else 16),
                 dtype=torch.int32,
             )
+        prompts = prompts_for(case, cfg["vocab"])
+        for chunk in CHUNKS:
+            served = reference_scheduled(spec, model, prompts, case["n_new"], 8 if tag == "b" else 16, chunk)
+            for i, tokens in enumerate(served):
+                out[f"served_chunk{chunk}_{i}"] = torch.tensor(tokens, dtype=torch.int32)
         save_file(out, str(HERE / f"golden_tiny_{tag}.safetensors"))
         print(f"tiny {tag}: max |reference - plain| = {worst:.3e}; logits scale {float(ref.abs().max()):.3f}")
 

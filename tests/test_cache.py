@@ -162,3 +162,30 @@ def test_random_orders_of_requests(seed):
         m.release(rid)
     m.check_invariants()
     assert m.free_pages() == [40, 25] and m.slots.num_free == 5
+
+
+def test_pools_for_keys_and_values_of_different_widths():
+    """A group may cache values narrower (or wider) than its keys, or none at all: the pools then are
+    two tensors, pages are counted and poisoned in both, and the bytes per token follow the widths."""
+    import torch
+
+    from edgerag_b200.cache.device import DevicePools
+
+    lay = CacheLayout(groups=[KVGroupSpec(2, 3, 16), KVGroupSpec(1, 1, 48, 0, v_head_dim=8), KVGroupSpec(1, 2, 24, 0, v_head_dim=0)],
+                      placement=[(0, 0), (1, 0), (0, 1), (2, 0)])
+    assert lay.bytes_per_token(2) == 2 * (2 * 3 * 32 + 1 * 1 * 56 + 1 * 2 * 24)
+    pools = DevicePools(lay, page_size=4, num_pages=[5, 6, 7], max_requests=2, dtype=torch.float32,
+                        device=torch.device("cpu"), poison=True)
+    k0, v0 = pools.pages_of(2)
+    assert k0.shape == v0.shape == (5, 3, 4, 16) and k0.data_ptr() != v0.data_ptr()
+    k1, v1 = pools.pages_of(1)
+    assert k1.shape == (6, 1, 4, 48) and v1.shape == (6, 1, 4, 8)
+    k2, v2 = pools.pages_of(3)
+    assert k2.shape == (7, 2, 4, 24) and v2.shape == (7, 2, 4, 0)
+    for t in (k0, v0, k1, v1, k2):
+        t.zero_()
+    pools.poison_pages([(1, 4), (0, 2), (2, 6)])
+    assert torch.isnan(k1[4]).all() and torch.isnan(v1[4]).all() and not torch.isnan(k1[:4]).any()
+    assert torch.isnan(k0[2]).all() and torch.isnan(v0[2]).all() and not torch.isnan(v0[3]).any()
+    assert torch.isnan(k2[6]).all() and not torch.isnan(k2[:6]).any()
+    assert pools.nbytes() == 4 * (5 * 2 * 2 * 3 * 4 * 16 + 6 * 4 * 56 + 7 * 2 * 4 * 24)

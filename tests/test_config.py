@@ -44,12 +44,35 @@ def test_kv_bytes_match_the_reference_figures():
     (lambda r: r.update(hidden_act="gelu"), "activation"),
     (lambda r: r.update(head_dim=15), "odd"),
     (lambda r: r.update(vocab_size=0), "positive"),
+    # options that change the arithmetic and are not built: refused by the key's name, never ignored
+    (lambda r: r.update(rope_scaling={"rope_type": "llama3", "factor": 8.0}), "rope_scaling"),
+    (lambda r: r.update(rope_scaling={"type": "linear", "factor": 2.0}), "rope_scaling"),
+    (lambda r: (r.pop("rope_theta"), r.update(rope_parameters={"rope_theta": 1e4, "rope_type": "yarn"})), "rope_type"),
+    (lambda r: (r.pop("rope_theta"), r.update(rope_parameters={"rope_theta": 1e4, "partial_rotary_factor": 0.5})), "partial_rotary"),
+    (lambda r: r.update(partial_rotary_factor=0.25), "partial_rotary"),
+    (lambda r: r.update(attention_bias=True), "attention_bias"),
+    (lambda r: r.update(mlp_bias=True), "mlp_bias"),
+    (lambda r: r.update(sliding_window=4096), "sliding_window"),
+    (lambda r: r.update(use_sliding_window=True, sliding_window=128), "sliding_window"),
+    (lambda r: r.update(final_logit_softcapping=30.0), "softcapping"),
 ])
 def test_bad_configs_are_refused(mutate, needle):
     raw = copy.deepcopy(plain.TINY_A)
     mutate(raw)
     with pytest.raises(ConfigError, match=needle):
         DecoderConfig.from_dict(raw)
+
+
+def test_neutral_values_of_unbuilt_options_are_accepted():
+    """What a stock Llama or SmolVLM config.json writes when the option is off must still load."""
+    raw = copy.deepcopy(plain.TINY_A)
+    raw.update(rope_scaling=None, attention_bias=False, mlp_bias=False, sliding_window=None, use_sliding_window=False)
+    assert DecoderConfig.from_dict(raw) == DecoderConfig.from_dict(plain.TINY_A)
+    raw.pop("rope_theta")
+    raw["rope_parameters"] = {"rope_theta": 10000.0, "rope_type": "default"}
+    assert DecoderConfig.from_dict(raw) == DecoderConfig.from_dict(plain.TINY_A)
+    raw.update(sliding_window=4096, use_sliding_window=False)      # a window that the config itself switches off
+    assert DecoderConfig.from_dict(raw) == DecoderConfig.from_dict(plain.TINY_A)
 
 
 def test_round_trip_and_folder(tmp_path):
@@ -83,4 +106,4 @@ def test_plan_names_every_size_from_the_config():
     assert mixer.kind == "attention" and mixer.params["n_kv_heads"] == 1 and mixer.params["head_dim"] == 32
     assert mixer.params["position"].params == {"head_dim": 32, "theta": 100000.0}
     assert plan.layers[0].norm1.params == {"size": 96, "eps": 1e-6}
-    assert plan.head.params["tied"] is False
+    assert plan.head.params["tied_to"] is None

@@ -73,7 +73,7 @@ def register_toy():
                                     PartSpec("swiglu", {"hidden": h, "intermediate": 2 * h}, "mlp.")))
         return ModelPlan(h, raw["vocab_size"], PartSpec("table", {"vocab": raw["vocab_size"], "hidden": h}, "embed_tokens."),
                          layers, [LayerCall(i, i) for i in range(len(layers))], norm("norm."),
-                         PartSpec("linear", {"vocab": raw["vocab_size"], "hidden": h, "tied": True}, "lm_head."))
+                         PartSpec("linear", {"vocab": raw["vocab_size"], "hidden": h, "tied_to": "embed_tokens.weight"}, "lm_head."))
 
     register_architecture("ToyDecayForCausalLM", read_config, make_plan)
 
@@ -175,7 +175,7 @@ def test_windowed_attention_layers_release_pages_behind_the_window(tmp_path):
                                    PartSpec("swiglu", {"hidden": h, "intermediate": inter}, "mlp.")))
         return ModelPlan(h, vocab, PartSpec("table", {"vocab": vocab, "hidden": h}, "embed_tokens."), specs,
                          [LayerCall(i, i) for i in range(layers)], norm("norm."),
-                         PartSpec("linear", {"vocab": vocab, "hidden": h, "tied": False}, "lm_head."))
+                         PartSpec("linear", {"vocab": vocab, "hidden": h, "tied_to": None}, "lm_head."))
 
     register_architecture("ToyWindowForCausalLM", lambda raw, where: raw, make_plan)
     raw = {"architectures": ["ToyWindowForCausalLM"]}

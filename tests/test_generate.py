@@ -54,6 +54,31 @@ def test_greedy_generation_matches_plain(which, dtype, model_folders):
         assert engine2.generate(prompts, SamplingParams(max_new_tokens=16)) == outs
 
 
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_tokens_of_the_reference_scheduler_and_executor(tag, tmp_path):
+    """The committed greedy tokens of the reference's own ``Scheduler`` + ``ModelExecutor`` serving the
+    golden prompts together with prompt portions of 4, 8 and 64 tokens (tests/golden/make_golden.py;
+    edgerag tests/test_executor.py:120-191): this engine, with the same portion sizes, generates them."""
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    from edgerag_b200 import Engine, SamplingParams
+
+    raw, seed, std, n_new = {"a": (plain.TINY_A, 0, 0.05, 16), "b": (plain.TINY_B, 1, 0.08, 8)}[tag]
+    folder = plain.write_model_folder(tmp_path / tag, raw, seed, std=std)
+    golden = load_file(str(Path(__file__).resolve().parent / "golden" / f"golden_tiny_{tag}.safetensors"))
+    n_prompts = sum(1 for key in golden if key.startswith("prompt_"))
+    prompts = [golden[f"prompt_{i}"].tolist() for i in range(n_prompts)]
+    for chunk in (4, 8, 64):
+        engine = Engine.from_pretrained(folder, dtype="float32", block_size=8 if tag == "b" else 16, num_blocks=64,
+                                        chunk_size=chunk, max_batch_size=n_prompts, max_prefills_per_step=1,
+                                        poison_freed_pages=True)
+        got = engine.generate(prompts, SamplingParams(max_new_tokens=n_new))
+        assert got == [golden[f"served_chunk{chunk}_{i}"].tolist() for i in range(n_prompts)], chunk
+        assert engine.cache.free_pages() == [64]
+
+
 def test_cuda_graph_decode_equals_eager_decode(model_folders):
     """Decode-only steps replay a captured CUDA graph; the tokens and logits are those of the eager path."""
     from edgerag_b200 import Engine, SamplingParams
@@ -153,6 +178,40 @@ def test_preemption_recomputes_to_the_same_tokens(model_folders):
     got = tight.generate(prompts, SamplingParams(max_new_tokens=40))
     assert tight.scheduler.stats.preempted >= 1 and got == want
     assert tight.cache.free_pages() == [7]
+
+
+def test_preemption_of_an_embedded_prompt_in_bfloat16(model_folders):
+    """The same in bfloat16 with the evicted request given as ``prompt_embeds``: when it is readmitted,
+    its embedded prompt is fed as rows again and its generated tokens as ids.  Recomputing in portions
+    rounds differently from decoding token by token, so the tokens must equal the roomy run's up to the
+    first place where the plain model's top-2 margin is not clear."""
+    from edgerag_b200 import Engine, SamplingParams
+
+    folder = model_folders("a", "bfloat16", std=0.2)
+    cfg, weights = plain.read_config(folder), plain.read_weights(folder)
+    ids = helpers.random_sequence(cfg["vocab"], 30, 1)
+    rows = torch.randn((30, cfg["hidden"]), generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    new = 40
+    roomy = Engine.from_pretrained(folder, dtype="bfloat16", block_size=16, num_blocks=32)
+    want = roomy.generate([ids, None], SamplingParams(max_new_tokens=new), prompt_embeds=[None, rows])
+    tight = Engine.from_pretrained(folder, dtype="bfloat16", block_size=16, num_blocks=7, overcommit=True,
+                                   max_prefills_per_step=2, poison_freed_pages=True)
+    got = tight.generate([ids, None], SamplingParams(max_new_tokens=new), prompt_embeds=[None, rows])
+    assert tight.scheduler.stats.preempted >= 1 and tight.request("req-1").preemptions >= 1
+    assert tight.cache.free_pages() == [7] and [len(g) for g in got] == [new, new]
+    heads = [plain.embed(weights, torch.tensor(ids)), rows.float()]
+    agreed = 0
+    for head, g, w in zip(heads, got, want):
+        if g == w:
+            agreed += new
+            continue
+        first = next(i for i in range(new) if g[i] != w[i])
+        agreed += first
+        embeds = torch.cat([head, plain.embed(weights, torch.tensor(w[:first]))]) if first else head
+        logits = plain.forward(weights, cfg, embeds=embeds)[-1]
+        top = torch.topk(logits, 2).values
+        assert float(top[0] - top[1]) <= 0.05 * float(logits.abs().max()), (first, g[first], w[first])
+    assert agreed >= new          # not vacuous: at least one request's worth of tokens agreed
 
 
 def test_command_line(model_folders, tmp_path):

@@ -401,6 +401,37 @@ def test_attention_decode_for_grouped_heads_on_tensor_cores(k, nq, nkv, ps, spli
     assert not k.decode_gqa_supported(dtype, 128, 0, nq, nkv, ps, split)
 
 
+@pytest.mark.parametrize("which", ["general", "bulk"])
+def test_attention_decode_merges_no_more_splits_than_it_was_sized_for(k, which):
+    """A caller that understates ``max_splits`` gets a wrong answer (only the first splits are merged),
+    but the merge must not walk past the scratch of its own (sequence, head): the floats behind it are
+    NaN here and would show in the result."""
+    dtype, nq, nkv, d, ps, split = torch.bfloat16, 4, 4, 64, 16, 128
+    ctx_lens = [700, 300]                       # 6 and 3 splits
+    case = paged_case(dtype, 55, nq, nkv, d, ps, ctx_lens, [1, 1])
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    understated = 2
+    acc_n, ml_n = k.decode_scratch_floats(2, nq, d, understated)
+    part_acc = torch.full((acc_n + 4096,), float("nan"), device="cuda")
+    part_ml = torch.full((ml_n + 4096,), float("nan"), device="cuda")
+    out = torch.full((2, nq * d), float("nan"), dtype=dtype, device="cuda")
+    tok = torch.arange(2, dtype=torch.int32).cuda()
+    if which == "general":
+        k.attention_decode(dev["q"], dev["kp"], dev["vp"], dev["tables"], tok, dev["pos"], out, nq, d ** -0.5,
+                           part_acc, part_ml, understated, split_keys=split)
+    else:
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        k.attention_decode_bulk(dev["q"], dev["kp"], dev["vp"], dev["tables"], tok, dev["pos"], out, nq, d ** -0.5,
+                                part_acc, part_ml, understated, status, split_keys=split)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert torch.isnan(part_acc[acc_n:]).all() and torch.isnan(part_ml[ml_n:]).all()
+    # what it merged is attention over the first two splits of each sequence
+    short = dict(case, pos=torch.tensor([2 * split - 1, 2 * split - 1], dtype=torch.int32))
+    want = attention_reference(short, nq, nkv, d, d ** -0.5)
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key(k, dtype):
     """One key far back, in the first page, gets a score that stands out: the output must be its value.
@@ -467,6 +498,96 @@ def test_attention_prefill_tensor_cores(k, nq, nkv, ps):
     out2 = torch.empty_like(out)
     k.attention_rows(dev["q"], dev["kp"], dev["vp"], dev["tables"], dev["seq_of"], dev["pos"], out2, nq, scale)
     torch.testing.assert_close(out.float(), out2.float(), atol=2e-2, rtol=2e-2)
+
+
+def plant_strong_keys(case, seq, nkv, d, ps, places, dtype, axis=5):
+    """Key ``p`` of sequence ``seq`` becomes ``b * e_axis`` for every ``(p, b)`` of ``places`` (in the
+    pages and in the plain copy).  A query row with ``q[axis] = 8`` then scores ``b`` on it at head size
+    64 (scale 1/8), far above the N(0, 1) scores of the random keys."""
+    for p, b in places:
+        page, off = int(case["tables"][seq, p // ps]), p % ps
+        key = torch.zeros(d)
+        key[axis] = b
+        for h in range(nkv):
+            case["ks"][seq][p, h] = key.to(dtype)
+            case["kp"][page, h, off] = key.to(dtype)
+
+
+@pytest.mark.parametrize("nq,nkv,ps", [(4, 2, 16), (2, 2, 8)])
+def test_attention_prefill_tensor_cores_when_row_maxima_jump(k, nq, nkv, ps):
+    """Random scores never move a row's maximum much after the first tile, so the path that rescales the
+    output accumulator when a maximum jumps would go untested.  Here keys with scores of 10, 25 and 40
+    (natural-log units: each more than 2^8 above everything before it) sit in later tiles of the keys, for
+    every third query row only, so that a warp holds rows that jump beside rows that do not; one sequence
+    continues from the cache with a strong key in the cached part and one in the new part."""
+    d, dtype = 64, torch.bfloat16
+    ctx_lens, q_lens = [1300, 700, 200], [1300, 257, 200]
+    case = paged_case(dtype, 333 + ps, nq, nkv, d, ps, ctx_lens, q_lens)
+    plant_strong_keys(case, 0, nkv, d, ps, [(300, 10.0), (600, 25.0), (1290, 40.0)], dtype)
+    plant_strong_keys(case, 1, nkv, d, ps, [(140, 10.0), (300, 25.0), (600, 40.0)], dtype)
+    plant_strong_keys(case, 2, nkv, d, ps, [(3, 40.0), (150, 10.0)], dtype)      # the strongest first: no jump later
+    q = case["q"].float().view(-1, nq, d)
+    q[::3, :, 5] = 8.0
+    case["q"] = q.view(-1, nq * d).to(dtype)
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    n_tok = dev["q"].shape[0]
+    qkv = torch.zeros((n_tok, (nq + 2 * nkv) * d), dtype=dtype, device="cuda")
+    qkv[:, : nq * d] = dev["q"]
+    starts = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32).cuda()
+    out = torch.full((n_tok, nq * d), float("nan"), dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.attention_prefill_tc(qkv, dev["kp"], dev["vp"], dev["tables"], starts, dev["pos"], out,
+                           sum(-(-n // 128) for n in q_lens), nq, scale, status)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    want = attention_reference(case, nq, nkv, d, scale)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+    # the planted keys decide the rows that look for them: row 1299 of sequence 0 is the value of key 1290
+    v_far = case["vs"][0][1290].float().repeat_interleave(nq // nkv, dim=0).reshape(-1)
+    assert float((got[1299] - v_far).abs().max()) < 0.03 and 1299 % 3 == 0
+    out2 = torch.empty_like(out)
+    k.attention_rows(dev["q"], dev["kp"], dev["vp"], dev["tables"], dev["seq_of"], dev["pos"], out2, nq, scale)
+    torch.testing.assert_close(out.float(), out2.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("which,nq,nkv,ps,split", [("bulk", 4, 4, 16, 512), ("bulk", 4, 4, 16, 2048), ("gqa", 6, 2, 16, 512),
+                                                   ("gqa", 15, 5, 16, 1024)])
+def test_decode_attention_finds_far_keys_and_follows_rising_maxima(k, which, nq, nkv, ps, split):
+    """The bulk-copy and the tensor-core decode kernels: one key in the first page decides a row; in
+    another row, keys of rising strength sit in later stages and later splits, so the running maximum
+    jumps inside a warp's stream, between the warps of a block and between splits."""
+    d, dtype = 64, torch.bfloat16
+    ctx_lens = [900, 1500, 1500, 77]
+    case = paged_case(dtype, 444 + nq, nq, nkv, d, ps, ctx_lens, [1] * 4)
+    plant_strong_keys(case, 0, nkv, d, ps, [(3, 18.0)], dtype)
+    plant_strong_keys(case, 1, nkv, d, ps, [(40, 10.0), (200, 25.0), (700, 40.0), (1400, 55.0)], dtype)
+    plant_strong_keys(case, 2, nkv, d, ps, [(1400, 10.0), (700, 25.0), (200, 40.0), (40, 55.0)], dtype)   # falling instead
+    q = case["q"].float().view(-1, nq, d)
+    q[:3, :, 5] = 8.0
+    case["q"] = q.view(-1, nq * d).to(dtype)
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    n = len(ctx_lens)
+    max_splits = max((c - 1) // split + 1 for c in ctx_lens)
+    acc_n, ml_n = k.decode_scratch_floats(n, nq, d, max_splits)
+    part_acc, part_ml = torch.full((acc_n,), float("nan"), device="cuda"), torch.full((ml_n,), float("nan"), device="cuda")
+    out = torch.full((n, nq * d), float("nan"), dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tok = torch.arange(n, dtype=torch.int32).cuda()
+    fn = k.attention_decode_bulk if which == "bulk" else k.attention_decode_gqa
+    fn(dev["q"], dev["kp"], dev["vp"], dev["tables"], tok, dev["pos"], out, nq, scale, part_acc, part_ml, max_splits,
+       status, split_keys=split)
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    want = attention_reference(case, nq, nkv, d, scale)
+    got = out.float().cpu()
+    torch.testing.assert_close(got, want, **tol(dtype))
+    for s, far in ((0, 3), (1, 1400), (2, 40)):
+        v_far = case["vs"][s][far].float().repeat_interleave(nq // nkv, dim=0).reshape(-1)
+        assert float((got[s] - v_far).abs().max()) < 0.04, (s, far)
 
 
 def test_attention_refuses_bad_head_sizes(k):

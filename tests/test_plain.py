@@ -29,6 +29,10 @@ def test_plain_matches_reference_decoder(tag, tmp_path):
         torch.testing.assert_close(logits[-want.shape[0]:], want, atol=1e-6, rtol=1e-6)
         greedy = plain.greedy_generate(weights, cfg, prompt, n_new)
         assert greedy == golden[f"greedy_{i}"].tolist()[:n_new]
+        # what the reference's scheduler and executor generate for the same prompts served together, in
+        # prompt portions of 4, 8 and 64 tokens (edgerag tests/test_executor.py:120-191)
+        for chunk in (4, 8, 64):
+            assert golden[f"served_chunk{chunk}_{i}"].tolist() == greedy
 
 
 def test_embeds_path_equals_ids_path(tmp_path):

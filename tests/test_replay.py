@@ -69,18 +69,20 @@ def test_first_tokens_and_long_decode(dtype, model_folders, tmp_path):
 
 
 def test_cuttings_agree_with_each_other_bf16(model_folders, tmp_path):
-    """In bfloat16 the cuttings differ from each other by rounding only, far less than from float32."""
+    """In bfloat16 the cuttings differ from each other by the rounding of a few sums only (the order in
+    which a product or a softmax adds its terms), far less than any of them differs from the 32-bit
+    plain model, where every activation's rounding counts.  The band is a few times the difference
+    that was measured, an order of magnitude below the band of the comparison with the plain model."""
     folder = model_folders("b", "bfloat16")
     cfg = plain.read_config(folder)
     seq = helpers.random_sequence(cfg["vocab"], 90, 11)
     trace = helpers.Trace()
-    trace.sequences.update({"w": seq, "p": seq})
+    trace.sequences.update({"w": seq, "p": seq, "t": seq})
     helpers.cut_whole(trace, "w")
     helpers.cut_portions(trace, "p")
+    helpers.cut_tail_decode(trace, "t", tail=32)
     results = helpers.run_trace(folder, "bfloat16", trace, tmp_path / "out", block_size=8)
-    rows = {}
-    for step, row, rid, pos in trace.expect:
-        rows[(rid, pos)] = results[step][row]
-    diff = max(float(np.abs(rows[("w", i)] - rows[("p", i)]).max()) for i in range(len(seq)))
-    scale = max(float(np.abs(rows[("w", i)]).max()) for i in range(len(seq)))
-    assert diff <= helpers.BF16_FRACTION * scale, (diff, scale)
+    stats = helpers.cuttings_agree(trace, results, ["w", "p", "t"], len(seq))
+    print("tiny b bfloat16, whole against portions and tail:", stats)
+    assert stats["max_fraction"] <= helpers.BF16_AGREE_FRACTION, stats
+    assert stats["mean_fraction"] <= helpers.BF16_AGREE_MEAN_FRACTION, stats

@@ -86,6 +86,41 @@ def test_prefixes_of_composite_checkpoints(tmp_path):
     assert torch.equal(got["embed_tokens.weight"], tensors["model.embed_tokens.weight"])
 
 
+def test_sharded_checkpoints_load_through_their_index(tmp_path):
+    """A folder with model.safetensors.index.json and shards gives the same tensors as the single file;
+    a shard the index names but the folder lacks, and a tensor missing from every shard, are reported."""
+    folder = plain.write_model_folder(tmp_path / "b", plain.TINY_B, 1)
+    tensors = {k: v.clone() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    cfg, model = _model(plain.TINY_B)
+    whole = load_safetensors(folder, model.weight_specs(), torch.float32, CPU)
+    names = sorted(tensors)
+    shards = {"model-00001-of-00003.safetensors": names[0::3], "model-00002-of-00003.safetensors": names[1::3],
+              "model-00003-of-00003.safetensors": names[2::3]}
+    (folder / "model.safetensors").unlink()
+    for shard, members in shards.items():
+        save_file({n: tensors[n] for n in members}, str(folder / shard))
+    index = {"metadata": {"total_size": 0}, "weight_map": {n: shard for shard, members in shards.items() for n in members}}
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    got = load_safetensors(folder, model.weight_specs(), torch.float32, CPU)
+    assert sorted(got) == sorted(whole) and all(torch.equal(got[n], whole[n]) for n in whole)
+
+    # a tensor that no shard holds: the one error, with its name
+    lost = "model.layers.1.mlp.up_proj.weight"
+    shard = index["weight_map"].pop(lost)
+    save_file({n: tensors[n] for n in shards[shard] if n != lost}, str(folder / shard))
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(WeightsError) as info:
+        load_safetensors(folder, model.weight_specs(), torch.float32, CPU)
+    assert info.value.missing == ["layers.1.mlp.up_proj.weight"]
+    # a shard file that is not there
+    (folder / "model-00002-of-00003.safetensors").unlink()
+    with pytest.raises(WeightsError, match="model-00002-of-00003.safetensors"):
+        load_safetensors(folder, model.weight_specs(), torch.float32, CPU)
+    # neither a single file nor an index
+    with pytest.raises(SafetensorsError, match="does not exist"):
+        load_safetensors(tmp_path / "nowhere", model.weight_specs(), torch.float32, CPU)
+
+
 def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
     cfg, model = _model(plain.TINY_A)
     folder = write_model_folder(tmp_path / "r", cfg.to_hf_dict(), model.weight_specs(), seed=3, dtype=torch.bfloat16)
