@@ -1,428 +1,17 @@
-// Causal attention for portions of prompts on the 5th-generation tensor cores (tcgen05 + TMEM).
-//
-// bfloat16, head size 64, queries of one (sequence, query head) in tiles of 128 rows, keys and
-// values read straight from cache pages in tiles of 128 keys.
-//
-//   S = Q K^T      tcgen05.mma  M=128 N=64 K=16 x4    A = Q tile, B = K tile, both K-major in
-//                  shared memory (rows of 128 bytes, 128-byte swizzle), accumulator in TMEM
-//   softmax        two threads per query row, 32 score columns each: tcgen05.ld of their part of the
-//                  S row, reference max / denominator in float, P rounded to bfloat16 into shared memory
-//   O += P V       tcgen05.mma  M=128 N=64 K=16 x4    A = P (K-major), B = V tile as stored in the
-//                  cache (rows = keys, 64 contiguous values: the MN-major operand form); O stays in TMEM
-//
-// K and V tiles of 64 keys are brought in with cp.async 16-byte copies (zero-filled past the last
-// visible key), two tiles ahead, four stages.  One block is 256 threads and 113 KB of shared
-// memory, so two blocks (16 warps) share an SM; each allocates 256 TMEM columns.
-//
-// Every wait on an mbarrier is bounded: on a timeout the block records an error in *status,
-// skips the rest of its work, frees its TMEM and returns.
-#include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-
-#include <map>
-#include <mutex>
-#include <tuple>
+// Decode attention (one new token per sequence) for bfloat16: keys and values streamed from the cache
+// pages by the asynchronous copy engines.  Two kernels share the split-KV scheme and the scratch layout
+// of the general kernel: one for a single query head per kv head (CUDA cores, bulk copies), one for
+// grouped query heads (tensor cores, TMA tensor copies).
 #include <stdarg.h>
-#include <stdint.h>
 #include <stdio.h>
 
 #undef ERB_ELEM
 #define ERB_ELEM 1
-#include "common.cuh"
+#include "tc_common.cuh"
 
 using namespace erb;
 
 ERB_DEFINE_LAST_ERROR(erb_last_error)
-
-namespace {
-
-constexpr int BM = 128;       // query rows per block
-constexpr int BN = 64;        // keys per tile
-constexpr int HD = 64;        // head size
-constexpr int kThreads = 256;     // two threads per query row
-constexpr int kKvStages = 4;      // K and V tiles in shared memory
-constexpr uint32_t kQBytes = BM * HD * 2;           // 16 KB: the Q tile
-constexpr uint32_t kTileBytes = BN * HD * 2;        // 8 KB: one K or V tile
-constexpr uint32_t kPBytes = BM * BN * 2;           // 16 KB: one P tile (two of them)
-// 114,752 bytes of tiles + 64 of barriers: two blocks fit in an SM's 227 KB (each block also costs 1 KB of
-// system shared memory), which needs the dynamic shared memory to start 1024-byte aligned: checked at run time.
-constexpr uint32_t kSmemBytes = kQBytes + 2 * kKvStages * kTileBytes + 2 * kPBytes + 64;
-constexpr uint32_t kTmemCols = 256;                 // S(even tiles): columns 0..63, S(odd): 64..127, O: 128..191
-constexpr uint32_t kSpinLimit = 1u << 20;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-// Byte offset of 16-byte chunk `c` (0..7) of row `r` in a tile of 128-byte rows with the
-// 128-byte swizzle: groups of 8 rows take 1024 bytes, the chunk index is XORed with the row.
-__device__ __forceinline__ uint32_t swz(int r, int c) {
-  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
-}
-
-// Shared-memory matrix descriptor: 128-byte swizzle, 1024 bytes between groups of 8 rows.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address, bits [0,14)
-  d |= (uint64_t)1 << 16;                           // leading byte offset (unused with this swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset, bits [32,46)
-  d |= (uint64_t)1 << 46;                           // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                           // layout: 128-byte swizzle
-  return d;
-}
-
-// Instruction descriptors: float accumulate, bfloat16 operands, M = 128.
-constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
-constexpr uint32_t kIdescO = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /*B is MN-major*/ |
-                             ((HD >> 3) << 17) | ((BM >> 4) << 24);
-
-__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-      "l"(a), "l"(b), "r"(idesc), "r"(acc)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-  uint32_t* r = reinterpret_cast<uint32_t*>(v);
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
-  const int n = valid ? 16 : 0;  // 0 bytes read: the 16 bytes are filled with zeros
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-// Waits for the phase with the given parity; gives up after kSpinLimit polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
-  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ float fast_exp2(float x) {          // 2^x, one instruction; -inf gives 0
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// Pipeline (one block, tile j of 64 keys):
-//   copies for tile j+2 are in flight (cp.async, four stages);
-//   S(j+1) = Q K(j+1)^T is issued before the softmax of tile j, into the other half of the S columns;
-//   the softmax of tile j reads S(j) from TMEM, writes P(j) (bfloat16) to one of two shared buffers;
-//   O += P(j) V(j) accumulates in TMEM and is only waited for when its inputs are reused two tiles
-//   later, or when the running maximum of a row grew by more than 2^8 and O must be rescaled.
-// The softmax keeps a reference maximum per row that only moves in such jumps (p <= 2^8 in between), so
-// the O rescale, the one step that would serialise the tensor core behind the CUDA cores, is rare.
-__global__ void __launch_bounds__(kThreads, 2)
-attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
-                            const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
-                            const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
-                            const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, int out_row_stride,
-                            int n_seqs, int nq, int nkv, int page_size, float scale_log2, int* __restrict__ status) {
-  chain_wait();
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const uint32_t base = smem_u32(smem_raw);
-  if (base & 1023u) {                       // the swizzled tiles need 1024-byte aligned bases
-    if (threadIdx.x == 0) atomicCAS(status, 0, 3000000);
-    return;
-  }
-  uint8_t* smem = smem_raw;
-  const uint32_t sQ = base, sK0 = base + kQBytes, sV0 = sK0 + kKvStages * kTileBytes, sP0 = sV0 + kKvStages * kTileBytes;
-  const uint32_t bar0 = sP0 + 2 * kPBytes;          // bar_s[0], bar_s[1], bar_pv[0], bar_pv[1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar0 - base) + 32);
-
-  // Two threads per query row: thread (row, half) owns score columns half*32 .. +31 of a tile and
-  // output columns half*32 .. +31.  A warp reaches the 32 TMEM lanes of its quarter.
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int row = tid & (BM - 1), half = tid >> 7;
-  const int h = blockIdx.y;
-  const int kvh = h / (nq / nkv);
-
-  // Which sequence and which 128-row tile of it this block owns.  Blocks are numbered from the last
-  // tile backwards: later tiles of a prompt see more keys and take longer, so they should start first.
-  int tile = (int)(gridDim.x - 1 - blockIdx.x), seq = -1, q0 = 0, rows = 0;
-  for (int s = 0; s < n_seqs; ++s) {
-    const int begin = seq_starts[s], len = seq_starts[s + 1] - begin;
-    const int n_tiles = (len + BM - 1) / BM;
-    if (tile < n_tiles) { seq = s; q0 = begin + tile * BM; rows = min(BM, len - tile * BM); break; }
-    tile -= n_tiles;
-  }
-  if (seq < 0) return;  // the grid was sized with an upper bound
-  if (*reinterpret_cast<volatile int*>(status) != 0) return;  // an earlier block gave up: do not pile on
-  const int pos0 = positions[q0];
-  const int last_key = pos0 + rows - 1;
-  const int n_kv = last_key / BN + 1;
-  const int* bt = block_tables + (size_t)seq * max_pages;
-
-  if (tid == 0) {
-#pragma unroll
-    for (int b = 0; b < 4; ++b) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8 * b));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-
-  // Each thread copies chunk (tid % 8) of rows (tid / 8) + 32 i, so a warp covers whole 128-byte rows.
-  const int lc = tid & 7, lr = tid >> 3;
-  const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
-  auto load_kv = [&](int j) {               // always commits a group, empty past the last tile
-    if (j < n_kv) {
-      const int stage = j % kKvStages;
-      const uint32_t dK = sK0 + stage * kTileBytes, dV = sV0 + stage * kTileBytes;
-#pragma unroll
-      for (int i = 0; i < BN / 32; ++i) {
-        const int r = lr + 32 * i;
-        const int key = j * BN + r;
-        const bool valid = key <= last_key;
-        size_t off = 0;
-        if (valid) {
-          const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
-          const int po = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-          off = (((size_t)bt[pi] * nkv + kvh) * page_size + po) * HD + lc * 8;
-        }
-        cp_async16(dK + swz(r, lc), k_pages + off, valid);
-        cp_async16(dV + swz(r, lc), v_pages + off, valid);
-      }
-    }
-    cp_async_commit();
-  };
-
-#pragma unroll
-  for (int i = 0; i < BM / 32; ++i) {
-    const int r = lr + 32 * i;
-    const bool valid = r < rows;
-    const __nv_bfloat16* src = q + (size_t)(q0 + (valid ? r : 0)) * q_row_stride + (size_t)h * HD + lc * 8;
-    cp_async16(sQ + swz(r, lc), src, valid);
-  }
-  load_kv(0);
-  load_kv(1);
-  cp_async_wait<1>();                       // Q and tile 0 have landed
-  fence_async_proxy();
-  fence_before_sync();
-  __syncthreads();
-  fence_after_sync();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes of TMEM
-  const uint32_t t_o = t_lane + 2 * BN + half * 32;                      // this thread's 32 output columns
-  const int my_pos = pos0 + row;
-  const uint64_t dq = make_desc(sQ);
-  bool ok = true;
-
-  auto issue_s = [&](int j) {               // thread 0: S(j) into S columns (j & 1) * 64
-    const uint64_t dk = make_desc(sK0 + (j % kKvStages) * kTileBytes);
-#pragma unroll
-    for (int k = 0; k < HD / 16; ++k) mma_bf16(tmem + (j & 1) * BN, dq + 2 * k, dk + 2 * k, kIdescS, k > 0);
-    mma_commit(bar0 + 8 * (j & 1));
-  };
-  if (tid == 0) issue_s(0);
-
-  float m_ref = -INFINITY, l_run = 0.f;     // l_run: this thread's half of the row's denominator
-  for (int j = 0; j < n_kv; ++j) {
-    // (A) tile j+1 is in shared memory for everyone; everyone is done with iteration j-1
-    cp_async_wait<0>();
-    fence_async_proxy();
-    fence_before_sync();
-    __syncthreads();
-    fence_after_sync();
-    if (tid == 0 && ok && j + 1 < n_kv) issue_s(j + 1);
-    // the stage tile j+2 goes into was last read by P V of tile j-2
-    if (ok && j >= 2 && !mbar_wait(bar0 + 16 + 8 * (j & 1), ((j - 2) >> 1) & 1)) ok = false;
-    load_kv(j + 2);
-
-    if (ok && !mbar_wait(bar0 + 8 * (j & 1), (j >> 1) & 1)) ok = false;
-    fence_after_sync();
-    float s[32];
-    if (ok) {
-      tmem_ld32(t_lane + (j & 1) * BN + half * 32, s);
-      tmem_ld_wait();
-    }
-    const int key0 = j * BN + half * 32;
-    float m_half = -INFINITY;
-    if (key0 + 31 <= my_pos) {              // every key of this half is visible to this row
-#pragma unroll
-      for (int i = 0; i < 32; ++i) m_half = fmaxf(m_half, s[i]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (key0 + i > my_pos) s[i] = -INFINITY;
-        m_half = fmaxf(m_half, s[i]);
-      }
-    }
-    m_half *= scale_log2;                   // scale > 0: the maximum of the scaled scores
-    // The two threads of a row exchange their maxima through the P buffer of this tile, which is free
-    // (P V of tile j-2 was waited for above): each writes into the first bytes of its partner's part of
-    // the row and reads its own part, which nobody else touches until the thread overwrites it with P.
-    uint8_t* p_row = smem + (sP0 - base) + (j & 1) * kPBytes;
-    *reinterpret_cast<float*>(p_row + swz(row, (half ^ 1) * 4)) = m_half;
-    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");   // only the two warps that share these rows
-    const float m_tile = fmaxf(m_half, *reinterpret_cast<const float*>(p_row + swz(row, half * 4)));
-    // The reference maximum moves only when the row's maximum grew by more than 2^8.
-    float alpha = 1.f;
-    const bool jump = m_tile > m_ref + 8.f;               // true on the first tile (m_ref = -inf)
-    if (jump) {
-      alpha = fast_exp2(m_ref - m_tile);                  // 0 on the first tile
-      m_ref = m_tile;
-    }
-    if (j > 0 && __any_sync(0xffffffffu, jump)) {
-      // O of this warp's rows is rescaled in TMEM; P V of tile j-1 must have landed first
-      if (ok && !mbar_wait(bar0 + 16 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1)) ok = false;
-      fence_after_sync();
-      if (ok) {
-        float acc[32];
-        tmem_ld32(t_o, acc);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] *= alpha;
-        tmem_st32(t_o, acc);
-        tmem_st_wait();
-      }
-    }
-    float l_tile = 0.f;
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {           // this thread's four 16-byte chunks of the row of P
-      uint32_t packed[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float p0 = fast_exp2(fmaf(s[8 * g + 2 * i], scale_log2, -m_ref));
-        const float p1 = fast_exp2(fmaf(s[8 * g + 2 * i + 1], scale_log2, -m_ref));
-        l_tile += p0 + p1;
-        __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-        packed[i] = *reinterpret_cast<uint32_t*>(&b);
-      }
-      if (ok) *reinterpret_cast<uint4*>(p_row + swz(row, half * 4 + g)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    }
-    l_run = l_run * alpha + l_tile;
-    fence_async_proxy();
-    fence_before_sync();
-    __syncthreads();                        // (B) P(j) is written, O is rescaled, S(j) has been read
-    if (tid == 0 && ok) {
-      fence_after_sync();
-      const uint64_t dp = make_desc(sP0 + (j & 1) * kPBytes), dv = make_desc(sV0 + (j % kKvStages) * kTileBytes);
-#pragma unroll
-      for (int k = 0; k < BN / 16; ++k)
-        mma_bf16(tmem + 2 * BN, dp + 2 * k, dv + (uint64_t)(k * (2048 >> 4)), kIdescO, (j > 0 || k > 0) ? 1u : 0u);
-      mma_commit(bar0 + 16 + 8 * (j & 1));
-    }
-  }
-  cp_async_wait<0>();
-  // every P V has landed once the last two have
-  if (ok && n_kv >= 2 && !mbar_wait(bar0 + 16 + 8 * ((n_kv - 2) & 1), ((n_kv - 2) >> 1) & 1)) ok = false;
-  if (ok && !mbar_wait(bar0 + 16 + 8 * ((n_kv - 1) & 1), ((n_kv - 1) >> 1) & 1)) ok = false;
-  fence_after_sync();
-  // exchange the two halves of the denominator (through P buffer 0: no P V reads it any more)
-  uint8_t* p_row = smem + (sP0 - base);
-  *reinterpret_cast<float*>(p_row + swz(row, (half ^ 1) * 4)) = l_run;
-  __syncthreads();
-  const float l_row = l_run + *reinterpret_cast<const float*>(p_row + swz(row, half * 4));
-
-  if (!ok) {
-    atomicCAS(status, 0, 1000000 + (int)blockIdx.x);
-  } else {
-    float acc[32];
-    tmem_ld32(t_o, acc);
-    tmem_ld_wait();
-    if (row < rows) {
-      const float inv = 1.f / l_row;
-      __nv_bfloat16* dst = out + (size_t)(q0 + row) * out_row_stride + (size_t)h * HD + half * (HD / 2);
-#pragma unroll
-      for (int d = 0; d < HD / 2; d += 8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 b = __floats2bfloat162_rn(acc[d + 2 * i] * inv, acc[d + 2 * i + 1] * inv);
-          w[i] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        *reinterpret_cast<uint4*>(dst + d) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
-  }
-  fence_before_sync();
-  __syncthreads();
-  if (warp == 0) {
-    fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
-  }
-}
-
-}  // namespace
-
-// Portions of prompts only (bfloat16, head_dim 64, no window).  q / out: row t is token t of the
-// batch; seq_starts: int32 [n_seqs + 1] token offsets of the sequences to process (consecutive
-// rows of block_tables); n_tiles: sum over them of ceil(length / 128) (an upper bound is fine).
-// status: device int, set non-zero if a block gave up waiting on the tensor cores.
-ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
-                                        const int* block_tables, int max_pages, const int* seq_starts,
-                                        const int* positions, void* out, int out_row_stride, int n_seqs,
-                                        int n_tiles, int nq, int nkv, int head_dim, int page_size, float scale,
-                                        int* status, void* stream) {
-  if (n_seqs <= 0 || n_tiles <= 0) return ERB_OK;
-  if (head_dim != HD) return fail(ERB_ERR_UNSUPPORTED, "attention_prefill_tc: head_dim %d (this kernel takes 64)", head_dim);
-  if (nq <= 0 || nkv <= 0 || nq % nkv || nq > 65535) return fail(ERB_ERR_ARG, "attention_prefill_tc: bad head counts");
-  if (page_size <= 0 || max_pages <= 0 || !status) return fail(ERB_ERR_ARG, "attention_prefill_tc: bad cache arguments");
-  if (q_row_stride % 8 || out_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
-      ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
-    return fail(ERB_ERR_UNSUPPORTED, "attention_prefill_tc: rows must be 16-byte aligned");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kSmemBytes);
-    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "attention_prefill_tc: %s", cudaGetErrorString(e));
-    configured = true;
-  }
-  const float scale_log2 = scale * 1.4426950408889634f;
-  launch_chained(attention_prefill_tc_kernel, dim3(dim3(n_tiles, nq)), dim3(kThreads), kSmemBytes, (cudaStream_t)stream, 
-      (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
-      block_tables, max_pages, seq_starts, positions, (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv,
-      page_size, scale_log2, status);
-  return check_launch("attention_prefill_tc");
-}
 
 // =============================================================================================
 // Decode attention (one new token per sequence) streamed with bulk asynchronous copies.
@@ -449,9 +38,6 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
-}
-__device__ __forceinline__ void mbar_expect(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Eight bfloat16 values (one 16-byte chunk of shared memory) as floats: a shift and a mask per pair.
 __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
@@ -839,11 +425,6 @@ constexpr int kGqaStages = 3;
 constexpr int kGqaMaxHeads = 8;                            // query heads per kv head (rows 0..7 of the tile)
 constexpr int kGqaThreads = kDecThreads + 32;               // eight multiplying warps and a copy warp
 
-__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, int row, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(bar) : "memory");
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t* r) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -1097,32 +678,6 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
 }
 
-// Tensor maps over a page pool [rows = pages * kv heads * page_size][64] with boxes of `box_rows`
-// rows, 128-byte swizzle.  Encoding is a host-side computation; the maps are kept per (pool, box).
-std::map<std::tuple<const void*, unsigned long long, unsigned>, CUtensorMap> g_maps;
-std::mutex g_maps_mutex;
-
-int pool_map(CUtensorMap* out, const void* pool, unsigned long long rows, unsigned box_rows) {
-  std::lock_guard<std::mutex> lock(g_maps_mutex);
-  const auto key = std::make_tuple(pool, rows, box_rows);
-  auto it = g_maps.find(key);
-  if (it == g_maps.end()) {
-    CUtensorMap m;
-    const cuuint64_t dims[2] = {64, rows};
-    const cuuint64_t strides[1] = {128};
-    const cuuint32_t box[2] = {64, box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = cuTensorMapEncodeTiled(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides,
-                                              box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(ERB_ERR_CUDA, "attention_decode_gqa: cuTensorMapEncodeTiled failed (%d)", (int)r);
-    if (g_maps.size() > 4096) g_maps.clear();
-    it = g_maps.emplace(key, m).first;
-  }
-  *out = it->second;
-  return ERB_OK;
-}
-
 }  // namespace
 
 // Whether erb_attention_decode_gqa takes these sizes (bfloat16 is implied).
@@ -1160,8 +715,8 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
   const unsigned long long rows = (unsigned long long)n_pool_pages * nkv * page_size;
   CUtensorMap mk, mv, mkl, mvl;
   int rc;
-  if ((rc = pool_map(&mk, k_pages, rows, (unsigned)(hg * page_size))) || (rc = pool_map(&mv, v_pages, rows, (unsigned)(hg * page_size))) ||
-      (rc = pool_map(&mkl, k_pages, rows, (unsigned)(last * page_size))) || (rc = pool_map(&mvl, v_pages, rows, (unsigned)(last * page_size))))
+  if ((rc = pool_map(&mk, k_pages, rows, (unsigned)(hg * page_size), "attention_decode_gqa")) || (rc = pool_map(&mv, v_pages, rows, (unsigned)(hg * page_size), "attention_decode_gqa")) ||
+      (rc = pool_map(&mkl, k_pages, rows, (unsigned)(last * page_size), "attention_decode_gqa")) || (rc = pool_map(&mvl, v_pages, rows, (unsigned)(last * page_size), "attention_decode_gqa")))
     return rc;
   const int r = nq / nkv;
   const size_t smem = 1024 + 2 * kGqaStages * kGqaStageBytes + 64 + (size_t)kDecWarps * r * (64 + 2) * sizeof(float) + 128 +

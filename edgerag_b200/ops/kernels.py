@@ -44,7 +44,7 @@ _SIGNATURES = {
     "erb_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                              c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_float, c_void_p],
-    "erb_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+    "erb_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                  c_void_p],
     "erb_attention_decode_bulk": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -498,31 +498,43 @@ def attention_decode_gqa(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
         launch_counts["own"] -= 1       # a single split writes the result itself: no second kernel
 
 
-def prefill_tc_supported(dtype: torch.dtype, head_dim: int, window: int) -> bool:
-    """Shapes the tensor-core prefill kernel takes; everything else goes to the general row kernel."""
-    return dtype == torch.bfloat16 and head_dim == 64 and window <= 0
+#: query rows of one (sequence, head) that a block of the tensor-core prefill kernel takes
+PREFILL_TC_ROWS = 256
+
+
+def prefill_tc_supported(dtype: torch.dtype, head_dim: int, window: int, page_size: int = 16) -> bool:
+    """Shapes the tensor-core prefill kernel takes (bfloat16, head size 64, no window, pages of 8 to
+    128 tokens, a power of two); everything else goes to the general row kernel."""
+    return (dtype == torch.bfloat16 and head_dim == 64 and window <= 0
+            and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0)
+
+
+def prefill_tc_blocks(q_lens) -> int:
+    """Blocks per head the tensor-core prefill kernel needs for portions of these lengths."""
+    return sum(-(-int(n) // PREFILL_TC_ROWS) for n in q_lens)
 
 
 def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
-                         seq_starts: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_tiles: int,
+                         seq_starts: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_blocks: int,
                          n_q_heads: int, scale: float, status: torch.Tensor) -> None:
     """Causal attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64, no window).
 
     ``qkv`` / ``out``: row t is token t of the batch (the q heads lead each qkv row);
     ``seq_starts`` int32 ``[n + 1]``: token offsets of the n sequences to process, whose block tables
-    are the n rows of ``block_tables``; ``n_tiles``: sum of ceil(length / 128) over them.
+    are the n rows of ``block_tables``; ``n_blocks``: ``prefill_tc_blocks`` of their lengths (an upper
+    bound is fine).
     """
     _need(qkv, "qkv", torch.bfloat16, contiguous=False); _need(k_pages, "k_pages", torch.bfloat16)
     _need(v_pages, "v_pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
     _need(seq_starts, "seq_starts", torch.int32); _need(positions, "positions", torch.int32)
     _need(out, "out", torch.bfloat16, contiguous=False); _need(status, "status", torch.int32)
-    _, nkv, page_size, d = k_pages.shape
+    n_pages, nkv, page_size, d = k_pages.shape
     n_seqs = seq_starts.numel() - 1
-    if qkv.stride(1) != 1 or out.stride(1) != 1 or block_tables.shape[0] < n_seqs:
+    if qkv.stride(1) != 1 or out.stride(1) != 1 or block_tables.shape[0] < n_seqs or v_pages.shape != k_pages.shape:
         raise KernelError("attention_prefill_tc: layout disagrees")
-    _call(_fn("attention_tc", None, "erb_attention_prefill_tc"), qkv.data_ptr(), qkv.stride(0), k_pages.data_ptr(),
-          v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_starts.data_ptr(),
-          positions.data_ptr(), out.data_ptr(), out.stride(0), n_seqs, int(n_tiles), n_q_heads, nkv, d, page_size,
+    _call(_fn("attention_prefill", None, "erb_attention_prefill_tc"), qkv.data_ptr(), qkv.stride(0), k_pages.data_ptr(),
+          v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], seq_starts.data_ptr(),
+          positions.data_ptr(), out.data_ptr(), out.stride(0), n_seqs, int(n_blocks), n_q_heads, nkv, d, page_size,
           float(scale), status.data_ptr(), _stream())
 
 

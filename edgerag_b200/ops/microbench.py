@@ -124,7 +124,7 @@ def prefill_attention(a) -> dict:
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     scale = a.head_dim ** -0.5
     if a.kernel == "tc":
-        fn = lambda: kernels.attention_prefill_tc(qkv, kp, vp, tables, starts, pos, out, -(-a.tokens // 128), a.heads,  # noqa: E731
+        fn = lambda: kernels.attention_prefill_tc(qkv, kp, vp, tables, starts, pos, out, kernels.prefill_tc_blocks([a.tokens]), a.heads,  # noqa: E731
                                                   scale, status)
     else:
         fn = lambda: kernels.attention_rows(qkv, kp, vp, tables, seq_of, pos, out, a.heads, scale)  # noqa: E731

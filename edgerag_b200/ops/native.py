@@ -32,6 +32,7 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...], bool]] = {
     "elementwise": ("elementwise.cu", (), True),
     "attention": ("attention.cu", (), True),
     "attention_tc": ("attention_tc.cu", ("-lcuda",), False),
+    "attention_prefill": ("attention_prefill.cu", ("-lcuda",), False),
     "gemm": ("gemm.cu", ("-lcublasLt",), True),
     "sampling": ("sampling.cu", (), False),
 }

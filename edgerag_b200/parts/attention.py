@@ -92,10 +92,9 @@ class Attention(Mixer):
                 kernels.attention_decode(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                          out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits,
                                          window=self.window, split_keys=split)
-        if n > nd and kernels.prefill_tc_supported(self.dtype, d, self.window):
-            n_tiles = sum(-(-q // 128) for q in ctx.host_q_len[nd:])
+        if n > nd and kernels.prefill_tc_supported(self.dtype, d, self.window, ctx.page_size):
             kernels.attention_prefill_tc(qkv, k_pages, v_pages, tables[nd:], ctx.seq_starts[nd:], ctx.positions, out,
-                                         n_tiles, self.n_q, self.scale, ctx.status)
+                                         kernels.prefill_tc_blocks(ctx.host_q_len[nd:]), self.n_q, self.scale, ctx.status)
         elif n > nd:
             kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:],
                                    out[nd:], self.n_q, self.scale, window=self.window)

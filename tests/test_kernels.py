@@ -486,7 +486,7 @@ def test_attention_prefill_tensor_cores(k, nq, nkv, ps):
     starts = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32).cuda()
     out = torch.full((n_tok, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    n_tiles = sum(-(-q // 128) for q in q_lens)
+    n_tiles = k.prefill_tc_blocks(q_lens)
     k.attention_prefill_tc(qkv, dev["kp"], dev["vp"], dev["tables"], starts, dev["pos"], out, n_tiles, nq, scale, status)
     torch.cuda.synchronize()
     assert int(status) == 0, f"the kernel gave up waiting on the tensor cores (status {int(status)})"
@@ -538,7 +538,7 @@ def test_attention_prefill_tensor_cores_when_row_maxima_jump(k, nq, nkv, ps):
     out = torch.full((n_tok, nq * d), float("nan"), dtype=dtype, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     k.attention_prefill_tc(qkv, dev["kp"], dev["vp"], dev["tables"], starts, dev["pos"], out,
-                           sum(-(-n // 128) for n in q_lens), nq, scale, status)
+                           k.prefill_tc_blocks(q_lens), nq, scale, status)
     torch.cuda.synchronize()
     assert int(status) == 0
     want = attention_reference(case, nq, nkv, d, scale)
