@@ -84,12 +84,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   auto bar = [&](int which) { return bars + 8u * (uint32_t)which; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.y;
+  const int h = blockIdx.x;
   const int kvh = h / (nq / nkv);
 
-  // Which sequence and which 256 rows of it this block owns.  Blocks are numbered from the last rows
-  // backwards: later rows of a prompt see more keys and take longer, so they should start first.
-  int tile = (int)(gridDim.x - 1 - blockIdx.x), seq = -1, q0 = 0, rows = 0;
+  // Which sequence and which 256 rows of it this block owns.  Blocks start in the order of their index,
+  // heads fastest: the last rows of every head first (later rows of a prompt see more keys and take
+  // longer), the first rows of every head last, so that the short blocks fill the gaps the long ones leave.
+  int tile = (int)(gridDim.y - 1 - blockIdx.y), seq = -1, q0 = 0, rows = 0;
   for (int s = 0; s < n_seqs; ++s) {
     const int begin = seq_starts[s], len = seq_starts[s + 1] - begin;
     const int n_tiles = (len + kRowsPerBlock - 1) / kRowsPerBlock;
@@ -105,7 +106,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     for (int s = 0; s < kVStages; ++s) { mbar_init(bar(kBarVFull + s), 1); mbar_init(bar(kBarVEmpty + s), 1); }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar(kBarSFull + t), 1);
-      mbar_init(bar(kBarPFull + t), kGroupThreads);
+      mbar_init(bar(kBarPFull + t), kGroupThreads / 32);   // one arrival per warp of the group
       mbar_init(bar(kBarPvDone + t), 1);
     }
     *s_abort = 0;
@@ -276,18 +277,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       fence_after_sync();
       const int key0 = j * BN + half * 64;
       const bool diagonal = j * BN + BN - 1 > pos0 + t * BM;             // some row of the tile has masked keys here
-      if (j > 0) {
-        // P V of tile j-1 has to be done before its P is overwritten, and before O is rescaled
-        wait(kBarPvDone + t, (j - 1) & 1);
-        if (!ok) break;
-        fence_after_sync();
-      }
       // The exponentials are taken against the reference maximum of the tiles before, without looking
       // for this tile's maximum first: P is a floating-point number, so a reference that is too low by
       // many powers of two costs no precision.  Only when a row's sum shows that the reference is far
       // too low (or on the first tile, which has none) is the maximum searched, the reference moved,
       // O and the running sum rescaled, and the tile's P computed again.
       float l_tile = 0.f;
+      uint32_t packed[32];
       bool search = j == 0;
       for (;;) {
         if (search) {
@@ -310,6 +306,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           }
           l_run *= alpha;
           if (j > 0) {
+            // O is rescaled in TMEM: P V of tile j-1 must have landed first
+            wait(kBarPvDone + t, (j - 1) & 1);
+            if (!ok) break;
+            fence_after_sync();
             float acc[32];
             tmem_ld32(t_o, acc);
             tmem_ld_wait();
@@ -319,36 +319,48 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           }
         }
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
+        // 16 keys at a time; the scores of the next 16 are on their way from TMEM while these are
+        // exponentiated.  P is collected in registers and stored once at the end, so that the wait for the
+        // second product of the tile before (whose P these stores overwrite) comes as late as possible.
+        float s[2][16];
+        tmem_ld16(t_s, s[0]);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {         // 32 keys at a time: 16 columns of P
-          float s[32];
-          tmem_ld32(t_s + 32 * c, s);
+        for (int c = 0; c < 4; ++c) {
           tmem_ld_wait();
+          if (c + 1 < 4) tmem_ld16(t_s + 16 * (c + 1), s[(c + 1) & 1]);
+          float* sc = s[c & 1];
           if (diagonal) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (key0 + 32 * c + i > my_pos) s[i] = -INFINITY;
+            for (int i = 0; i < 16; ++i)
+              if (key0 + 16 * c + i > my_pos) sc[i] = -INFINITY;
           }
-          uint32_t packed[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(s[2 * i], scale_log2, -m_ref));
-            const float p1 = fast_exp2(fmaf(s[2 * i + 1], scale_log2, -m_ref));
+          for (int i = 0; i < 8; ++i) {
+            const float p0 = fast_exp2(fmaf(sc[2 * i], scale_log2, -m_ref));
+            const float p1 = fast_exp2(fmaf(sc[2 * i + 1], scale_log2, -m_ref));
             l4[i & 3] += p0 + p1;
             __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-            packed[i] = *reinterpret_cast<uint32_t*>(&b);
+            packed[8 * c + i] = *reinterpret_cast<uint32_t*>(&b);
           }
-          tmem_st16(t_p + 16 * c, packed);
         }
         l_tile = (l4[0] + l4[1]) + (l4[2] + l4[3]);
         // both threads of a row have to agree on the reference: the two warps decide together
         if (search || !named_barrier_any(pair_barrier, 64, !(l_tile < kSumLimit))) break;
         search = true;
       }
+      if (!ok) break;
+      if (j > 0) {
+        // P V of tile j-1 has to be done before its P is overwritten
+        wait(kBarPvDone + t, (j - 1) & 1);
+        if (!ok) break;
+        fence_after_sync();
+      }
+      tmem_st32(t_p, reinterpret_cast<const float*>(packed));
       tmem_st_wait();
       l_run += l_tile;
       fence_before_sync();
-      mbar_arrive(bar(kBarPFull + t));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kBarPFull + t));
     }
     if (n_t[t] > 0) {
       wait(kBarPvDone + t, (n_t[t] - 1) & 1);
@@ -386,7 +398,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       for (int i = max(0, copies_k - kKStages); i < copies_k; ++i) mbar_wait(bar(kBarKFull + (i & (kKStages - 1))), (i / kKStages) & 1);
       for (int i = max(0, copies_v - kVStages); i < copies_v; ++i) mbar_wait(bar(kBarVFull + (i & (kVStages - 1))), (i / kVStages) & 1);
     }
-    if (tid == 0) atomicCAS(status, 0, 1000000 + (int)blockIdx.x);
+    if (tid == 0) atomicCAS(status, 0, 1000000 + (int)(blockIdx.y * gridDim.x + blockIdx.x));
     __syncthreads();
   }
   if (warp == kIssueWarp) {
@@ -419,7 +431,7 @@ ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const v
   if (!erb_attention_prefill_tc_supported(head_dim, page_size))
     return fail(ERB_ERR_UNSUPPORTED, "attention_prefill_tc: head_dim %d with pages of %d (takes 64 with 8, 16, 32, 64 or 128)",
                 head_dim, page_size);
-  if (nq <= 0 || nkv <= 0 || nq % nkv || nq > 65535) return fail(ERB_ERR_ARG, "attention_prefill_tc: bad head counts");
+  if (nq <= 0 || nkv <= 0 || nq % nkv || n_blocks > 65535) return fail(ERB_ERR_ARG, "attention_prefill_tc: bad head counts or too many blocks");
   if (max_pages <= 0 || !status || n_pool_pages <= 0) return fail(ERB_ERR_ARG, "attention_prefill_tc: bad cache arguments");
   if (q_row_stride % 8 || out_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
       ((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127))
@@ -440,7 +452,7 @@ ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const v
     configured = true;
   }
   const float scale_log2 = scale * 1.4426950408889634f;
-  launch_chained(attention_prefill_kernel, dim3(n_blocks, nq), dim3(kThreads), kSmemBytes, (cudaStream_t)stream, mk, mv,
+  launch_chained(attention_prefill_kernel, dim3(nq, n_blocks), dim3(kThreads), kSmemBytes, (cudaStream_t)stream, mk, mv,
                  (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, seq_starts, positions,
                  (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv, page_size, scale_log2, status);
   return check_launch("attention_prefill_tc");
