@@ -332,6 +332,8 @@ class ModelRunner:
         # pages given back since the last step are overwritten before any of them is handed out again
         self.pools.poison_pages(self.cache.drain_freed())
         ctx, ordered = self.prepare(entries)
+        if self.dtype == torch.bfloat16:
+            kernels.linear_status_word(self.status)      # (the products report to this runner's word)
         if ctx.n_fed_back:
             kernels.resolve_ids(ctx.token_ids, self.feedback, self.dtype)
         logits = self._forward(ctx)
@@ -355,7 +357,8 @@ class ModelRunner:
             self._status_host.zero_()
             if code >= 1000000:
                 raise StepError(f"an attention kernel gave up (code {code}: 1xxxxxx prefill wait, 2xxxxxx decode "
-                                "wait, 3000000 shared-memory alignment); the step's results are not valid")
+                                "wait, 3000000 shared-memory alignment, 4xxxxxx a wait of a product for few rows); "
+                                "the step's results are not valid")
             raise StepError(f"a kernel flagged token {code - 1} of the batch (id or row out of range)")
 
     def drop_graphs(self) -> None:

@@ -39,6 +39,10 @@ _SIGNATURES = {
     "erb_linear_skinny_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_skinny_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "erb_linear_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_linear_tc_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_linear_tc_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "erb_attention_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "erb_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -61,7 +65,8 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
 _LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 2, "erb_attention_decode_gqa": 2, "erb_linear": 0}
-SKINNY_MAX_ROWS = 16
+SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
+TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
 
 
 def _fn(library: str, elem: str | None, name: str):
@@ -227,6 +232,22 @@ def _workspace(device: torch.device) -> torch.Tensor:
     return ws
 
 
+_set_status_word = None
+
+
+def linear_status_word(status: torch.Tensor | None) -> None:
+    """Name the device word (int32) to which the TMA + tcgen05 weight-streaming kernel reports a wait
+    that ran out (code 4000000 + block).  Kept until named again."""
+    global _set_status_word
+    if status is not None:
+        _need(status, "status", torch.int32)
+    if _set_status_word is None:
+        _set_status_word = native.load("linear_tc", None).erb_linear_tc_set_status_word
+        _set_status_word.argtypes = [c_void_p]
+        _set_status_word.restype = c_int
+    _set_status_word(_ptr(status))
+
+
 def linear_few_rows_supported(a: torch.Tensor, weight: torch.Tensor, lda: int) -> bool:
     """Whether the weight-streaming kernel takes these operands (bfloat16, at most 64 rows, 16-byte rows)."""
     k = a.shape[1]
@@ -235,8 +256,7 @@ def linear_few_rows_supported(a: torch.Tensor, weight: torch.Tensor, lda: int) -
 
 
 def linear_few_rows(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """``linear`` through the weight-streaming kernel, for up to 64 rows (``linear`` itself switches to the
-    library above ``SKINNY_MAX_ROWS``, where the library is faster)."""
+    """``linear`` through the weight-streaming kernel, for up to 64 rows."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
     _need(out, "out", contiguous=False)
     m, k = a.shape
@@ -251,10 +271,63 @@ def linear_few_rows(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) ->
           lda, k, ldo, int(out.dtype == torch.float32), _stream())
 
 
-def linear_glu_supported(a: torch.Tensor, weight: torch.Tensor) -> bool:
-    """Whether ``linear_glu`` takes these operands: a handful of bfloat16 rows, 16-byte rows."""
+def linear_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``linear`` for up to 64 bfloat16 rows through the TMA + tcgen05 weight-streaming kernel."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
+    _need(out, "out", contiguous=False)
+    m, k = a.shape
+    n = weight.shape[0]
+    lda = a.stride(0) if m > 1 else max(k, a.stride(0))
+    ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
+    if weight.shape[1] != k or out.shape != (m, n) or a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("linear_tc: shapes or strides disagree")
+    if out.dtype not in (torch.bfloat16, torch.float32) or not linear_few_rows_supported(a, weight, lda):
+        raise KernelError("linear_tc: operands not supported")
+    _call(_fn("linear_tc", None, "erb_linear_tc"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, lda, k, ldo,
+          int(out.dtype == torch.float32), _stream())
+
+
+def linear_tc_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``linear_glu`` through the TMA + tcgen05 kernel."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
+    _need(out, "out", torch.bfloat16, contiguous=False)
+    m, k = a.shape
+    n = weight.shape[0] // 2
+    if weight.shape[1] != k or out.shape != (m, n) or a.stride(1) != 1 or out.stride(1) != 1 or not linear_glu_supported(a, weight, 64):
+        raise KernelError("linear_tc_glu: shapes, strides or operands not supported")
+    lda = a.stride(0) if m > 1 else max(k, a.stride(0))
+    ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
+    _call(_fn("linear_tc", None, "erb_linear_tc_glu"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, lda, k, ldo,
+          _stream())
+
+
+def linear_tc_rope_store(a: torch.Tensor, weight: torch.Tensor, qkv: torch.Tensor, positions: torch.Tensor,
+                         inv_freq: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, slots: torch.Tensor,
+                         k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int) -> None:
+    """``linear_rope_store`` through the TMA + tcgen05 kernel (head sizes 32, 64, 128)."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
+    _need(qkv, "qkv", torch.bfloat16, contiguous=False); _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32); _need(slots, "slots", torch.int32)
+    _need(k_pages, "k_pages", torch.bfloat16); _need(v_pages, "v_pages", torch.bfloat16)
+    m, k = a.shape
+    width = (n_q_heads + 2 * n_kv_heads) * head_dim
+    if (weight.shape != (width, k) or qkv.shape != (m, width) or a.stride(1) != 1 or qkv.stride(1) != 1
+            or positions.numel() < m or slots.numel() < m or inv_freq.numel() != head_dim // 2
+            or k_pages.shape[1:] != (n_kv_heads, page_size, head_dim) or v_pages.shape != k_pages.shape
+            or head_dim not in (32, 64, 128) or not linear_rope_store_supported(a, weight, head_dim, head_dim, 64)):
+        raise KernelError("linear_tc_rope_store: shapes, strides or operands not supported")
+    lda = a.stride(0) if m > 1 else max(k, a.stride(0))
+    ldo = qkv.stride(0) if m > 1 else max(width, qkv.stride(0))
+    _call(_fn("linear_tc", None, "erb_linear_tc_rope"), a.data_ptr(), weight.data_ptr(), qkv.data_ptr(), m, k, lda, k, ldo,
+          n_q_heads, n_kv_heads, head_dim, positions.data_ptr(), inv_freq.data_ptr(), slots.data_ptr(),
+          k_pages.data_ptr(), v_pages.data_ptr(), page_size, _stream())
+
+
+def linear_glu_supported(a: torch.Tensor, weight: torch.Tensor, max_rows: int = SKINNY_MAX_ROWS) -> bool:
+    """Whether the gated products take these operands: a handful of bfloat16 rows (``max_rows``: 16 where
+    the register-fed kernel is the better choice, up to 64 for the kernels' own limit), 16-byte rows."""
     lda = a.stride(0) if a.shape[0] > 1 else max(a.shape[1], a.stride(0))
-    return a.shape[0] <= SKINNY_MAX_ROWS and weight.shape[0] % 2 == 0 and linear_few_rows_supported(a, weight, lda)
+    return a.shape[0] <= max_rows and weight.shape[0] % 2 == 0 and linear_few_rows_supported(a, weight, lda)
 
 
 def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -265,7 +338,7 @@ def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None
     _need(out, "out", torch.bfloat16, contiguous=False)
     m, k = a.shape
     n = weight.shape[0] // 2
-    if weight.shape[1] != k or out.shape != (m, n) or a.stride(1) != 1 or out.stride(1) != 1 or not linear_glu_supported(a, weight):
+    if weight.shape[1] != k or out.shape != (m, n) or a.stride(1) != 1 or out.stride(1) != 1 or not linear_glu_supported(a, weight, 64):
         raise KernelError("linear_glu: shapes, strides or operands not supported")
     lda = a.stride(0) if m > 1 else max(k, a.stride(0))
     ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
@@ -273,11 +346,12 @@ def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None
           lda, k, ldo, _stream())
 
 
-def linear_rope_store_supported(a: torch.Tensor, weight: torch.Tensor, head_dim: int, rot_dim: int) -> bool:
-    """Whether ``linear_rope_store`` takes these operands: a handful of bfloat16 rows, full rotation,
-    head sizes in steps of 16."""
+def linear_rope_store_supported(a: torch.Tensor, weight: torch.Tensor, head_dim: int, rot_dim: int,
+                                max_rows: int = SKINNY_MAX_ROWS) -> bool:
+    """Whether the products with the rotary epilogue take these operands: a handful of bfloat16 rows
+    (``max_rows`` as for ``linear_glu_supported``), full rotation, head sizes in steps of 16."""
     lda = a.stride(0) if a.shape[0] > 1 else max(a.shape[1], a.stride(0))
-    return (a.shape[0] <= SKINNY_MAX_ROWS and rot_dim == head_dim and head_dim % 16 == 0
+    return (a.shape[0] <= max_rows and rot_dim == head_dim and head_dim % 16 == 0
             and linear_few_rows_supported(a, weight, lda))
 
 
@@ -296,7 +370,7 @@ def linear_rope_store(a: torch.Tensor, weight: torch.Tensor, qkv: torch.Tensor, 
     if (weight.shape != (width, k) or qkv.shape != (m, width) or a.stride(1) != 1 or qkv.stride(1) != 1
             or positions.numel() < m or slots.numel() < m or inv_freq.numel() != head_dim // 2
             or k_pages.shape[1:] != (n_kv_heads, page_size, head_dim) or v_pages.shape != k_pages.shape
-            or not linear_rope_store_supported(a, weight, head_dim, head_dim)):
+            or not linear_rope_store_supported(a, weight, head_dim, head_dim, 64)):
         raise KernelError("linear_rope_store: shapes, strides or operands not supported")
     lda = a.stride(0) if m > 1 else max(k, a.stride(0))
     ldo = qkv.stride(0) if m > 1 else max(width, qkv.stride(0))
@@ -305,8 +379,14 @@ def linear_rope_store(a: torch.Tensor, weight: torch.Tensor, qkv: torch.Tensor, 
           k_pages.data_ptr(), v_pages.data_ptr(), page_size, _stream())
 
 
-def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-    """out[M, N] (+)= a[M, K] @ weight[N, K]^T (library product, float accumulation, no TF32).
+def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+           library: bool = False) -> None:
+    """out[M, N] (+)= a[M, K] @ weight[N, K]^T (float accumulation, no TF32).  bfloat16 rows of a
+    decode step go through this package's weight-streaming kernels: up to ``SKINNY_MAX_ROWS`` rows the
+    register-fed one, up to ``TC_MAX_ROWS`` rows the TMA + tcgen05 one where the product has enough
+    rows of w to give every SM a block without a split over k (the output head).  Within each of the
+    two a row's bits do not depend on how many other rows the step has.  Everything else, or all with
+    ``library=True``, is a library product.
 
     ``a`` and ``out`` may be row-strided views (last dimension contiguous); ``out`` is float or the
     element type of ``a``.
@@ -322,11 +402,16 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate:
         return
     lda = a.stride(0) if m > 1 else max(k, a.stride(0))
     ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
-    if m <= SKINNY_MAX_ROWS and not accumulate and linear_few_rows_supported(a, weight, lda):
-        # a handful of rows: this package's weight-streaming kernel instead of the library product
-        _call(_fn("gemm", "bfloat16", "erb_linear_skinny"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
-              lda, k, ldo, int(out.dtype == torch.float32), _stream())
-        return
+    if m <= TC_MAX_ROWS and not accumulate and not library and linear_few_rows_supported(a, weight, lda):
+        if m <= SKINNY_MAX_ROWS:
+            # a handful of rows: this package's weight-streaming kernel instead of the library product
+            _call(_fn("gemm", "bfloat16", "erb_linear_skinny"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+                  lda, k, ldo, int(out.dtype == torch.float32), _stream())
+            return
+        if n >= 128 * 2 * _sms(a.device):
+            _call(_fn("linear_tc", None, "erb_linear_tc"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+                  lda, k, ldo, int(out.dtype == torch.float32), _stream())
+            return
     ws = _workspace(a.device)
     _call(_fn("gemm", _elem(a), "erb_linear"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
           lda, k, ldo, int(out.dtype == torch.float32), int(accumulate), ws.data_ptr(), ws.numel(), _stream())
@@ -359,6 +444,14 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
 
 
 _sm_counts: dict[int, int] = {}
+
+
+def _sms(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch._C._cuda_getDevice()
+    n = _sm_counts.get(idx)
+    if n is None:
+        n = _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
 
 
 def choose_decode_split(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int, head_dim: int = 64) -> int:

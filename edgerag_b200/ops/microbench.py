@@ -141,16 +141,22 @@ def linear(a) -> dict:
     ws = [torch.randn((a.n, a.k), device="cuda").to(dtype) for _ in range(reps)]
     x = torch.randn((a.m, a.k), device="cuda").to(dtype)
     out = torch.empty((a.m, a.n), device="cuda", dtype=torch.float32 if a.out32 else dtype)
+    out_glu = torch.empty((a.m, a.n // 2), device="cuda", dtype=dtype) if a.glu else None
     state = {"i": 0}
 
     def fn():
         state["i"] = (state["i"] + 1) % reps
-        (kernels.linear_few_rows if a.few_rows else kernels.linear)(x, ws[state["i"]], out)
+        if a.tc:
+            (kernels.linear_tc_glu if a.glu else kernels.linear_tc)(x, ws[state["i"]], out_glu if a.glu else out)
+        elif a.glu:
+            kernels.linear_glu(x, ws[state["i"]], out_glu)
+        else:
+            kernels.linear(x, ws[state["i"]], out, library=a.library)
 
     us = _time(fn, a.iters, a.warmup)
     nbytes = a.n * a.k * x.element_size() + a.m * a.k * x.element_size() + out.numel() * out.element_size()
     flops = 2.0 * a.m * a.n * a.k
-    return {"case": "linear", "m": a.m, "n": a.n, "k": a.k, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+    return {"case": "linear", "m": a.m, "n": a.n, "k": a.k, "library": bool(a.library), "tc": bool(a.tc), "glu": bool(a.glu), "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
             "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4), "tflops": round(flops / us / 1e6, 2)}
 
 
@@ -239,7 +245,9 @@ def main(argv=None) -> int:
     g.add_argument("--n", type=int, default=6144)
     g.add_argument("--k", type=int, default=2048)
     g.add_argument("--out32", action="store_true")
-    g.add_argument("--few-rows", action="store_true", help="force the weight-streaming kernel (up to 64 rows)")
+    g.add_argument("--library", action="store_true", help="force the library product (cuBLASLt) also for few rows")
+    g.add_argument("--tc", action="store_true", help="the TMA + tcgen05 weight-streaming kernel (up to 64 rows)")
+    g.add_argument("--glu", action="store_true", help="the gated product: w is [gate; up] of n rows, out has n / 2 columns")
     k = sub.add_parser("step-kernels", parents=[common])
     k.add_argument("--layers", type=int, default=4)
     k.add_argument("--batch", type=int, default=8)

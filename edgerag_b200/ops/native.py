@@ -34,6 +34,7 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...], bool]] = {
     "attention_tc": ("attention_tc.cu", ("-lcuda",), False),
     "attention_prefill": ("attention_prefill.cu", ("-lcuda",), False),
     "gemm": ("gemm.cu", ("-lcublasLt",), True),
+    "linear_tc": ("linear_tc.cu", ("-lcuda",), False),
     "sampling": ("sampling.cu", (), False),
 }
 

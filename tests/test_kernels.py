@@ -202,12 +202,13 @@ def test_gated_product_equals_product_then_gate(k):
     """The decode step's gate/up product with the gate in its epilogue gives, bit for bit, what the
     plain product into a [M, 2N] buffer followed by the gate kernel gives, and both follow the
     formula silu(x Wg^T) * (x Wu^T); N no multiple of the 8 gate rows a block takes, K no multiple of a pass."""
-    for m, n, kk in ((1, 96, 64), (8, 8192 // 4, 2048), (5, 203, 1032), (16, 77, 264), (11, 1024, 4096)):
+    for m, n, kk in ((1, 96, 64), (8, 8192 // 4, 2048), (5, 203, 1032), (16, 77, 264), (11, 1024, 4096), (17, 203, 1032),
+                     (40, 2048, 2048), (64, 77, 264), (33, 1024, 4096)):
         a = rand((m, kk), torch.bfloat16, 70 + m, 0.5)
         w = rand((2 * n, kk), torch.bfloat16, 71 + m, 0.3)
-        assert k.linear_glu_supported(a, w)
+        assert k.linear_glu_supported(a, w, 64) and k.linear_glu_supported(a, w) == (m <= 16)
         both = torch.empty((m, 2 * n), dtype=torch.bfloat16, device="cuda")
-        k.linear(a, w, both)
+        k.linear_few_rows(a, w, both)
         two_steps = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
         k.swiglu(both, two_steps)
         fused = torch.full((m, n + 5), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :n]
@@ -216,7 +217,7 @@ def test_gated_product_equals_product_then_gate(k):
         g, u = (a.double() @ w.double().T).split(n, dim=1)
         want = torch.nn.functional.silu(g) * u
         torch.testing.assert_close(fused.double(), want, atol=0.02 * (kk ** 0.5) / 8, rtol=0.02)
-    assert not k.linear_glu_supported(rand((17, 64), torch.bfloat16, 1), rand((32, 64), torch.bfloat16, 2))
+    assert not k.linear_glu_supported(rand((65, 64), torch.bfloat16, 1), rand((32, 64), torch.bfloat16, 2))
     assert not k.linear_glu_supported(rand((4, 64), torch.float32, 1), rand((32, 64), torch.float32, 2))
 
 
@@ -224,7 +225,8 @@ def test_projection_with_rotation_and_cache_write_equals_the_three_steps(k):
     """The decode step's q/k/v product with the rotary encoding and the cache write in its epilogue
     leaves, bit for bit, the q columns and the cache pages that the product, then the rotation
     kernel leave; a token with a negative slot writes no key or value."""
-    for m, nq, nkv, d, kk, ps in ((1, 4, 2, 16, 64, 4), (8, 32, 32, 64, 2048, 16), (5, 9, 3, 48, 264, 8), (16, 6, 1, 128, 1032, 16)):
+    for m, nq, nkv, d, kk, ps in ((1, 4, 2, 16, 64, 4), (8, 32, 32, 64, 2048, 16), (5, 9, 3, 48, 264, 8), (16, 6, 1, 128, 1032, 16),
+                                  (17, 9, 3, 48, 264, 8), (64, 32, 32, 64, 2048, 16), (37, 15, 5, 64, 960, 16)):
         width = (nq + 2 * nkv) * d
         a = rand((m, kk), torch.bfloat16, 80 + m, 0.5)
         w = rand((width, kk), torch.bfloat16, 81 + m, 0.3)
@@ -235,7 +237,7 @@ def test_projection_with_rotation_and_cache_write_equals_the_three_steps(k):
         if m > 2:
             slots[2] = -1
         slots = slots.cuda()
-        assert k.linear_rope_store_supported(a, w, d, d)
+        assert k.linear_rope_store_supported(a, w, d, d, 64) and k.linear_rope_store_supported(a, w, d, d) == (m <= 16)
         results = []
         for fused in (False, True):
             kp = torch.full((n_pages, nkv, ps, d), 7.0, dtype=torch.bfloat16, device="cuda")
@@ -244,13 +246,92 @@ def test_projection_with_rotation_and_cache_write_equals_the_three_steps(k):
             if fused:
                 k.linear_rope_store(a, w, qkv, positions, inv_freq, nq, nkv, d, slots, kp, vp, ps)
             else:
-                k.linear(a, w, qkv)
+                k.linear_few_rows(a, w, qkv)
                 k.rope_cache_write(qkv, positions, inv_freq, nq, nkv, d, d, slots=slots, k_pages=kp, v_pages=vp, page_size=ps)
             results.append((qkv[:, : nq * d].clone(), kp, vp))
         for two, one in zip(*results):
             assert torch.equal(two, one)
         assert float(results[1][1].float().sub(7.0).abs().sum()) > 0      # something was written
     assert not k.linear_rope_store_supported(rand((4, 64), torch.bfloat16, 1), rand((96, 64), torch.bfloat16, 2), 16, 8)
+
+
+def test_tensor_core_products_for_few_rows(k):
+    """The TMA + tcgen05 weight-streaming kernel for up to 64 rows: plain products against float64 (N and K
+    no multiples of a tile, float and bfloat16 out), the gated and the rotating epilogues bit-equal to
+    product-then-kernel, products split over k by a cluster, and a row's bits the same whatever the
+    number of rows."""
+    for m, n, kk in ((8, 6144, 2048), (1, 96, 64), (16, 257, 1032), (5, 2048, 8192), (64, 100, 72), (29, 311, 264),
+                     (64, 2048, 2048), (33, 49155 // 7, 2048), (48, 16384, 2048)):
+        a, w = rand((m, kk), torch.bfloat16, 140 + m, 0.5), rand((n, kk), torch.bfloat16, 141 + m, 0.5)
+        want = a.double() @ w.double().T
+        out = torch.full((m, n + 3), float("nan"), dtype=torch.float32, device="cuda")[:, :n]
+        k.linear_tc(a, w, out)
+        torch.testing.assert_close(out.double(), want, atol=2e-3 * (kk ** 0.5) / 8, rtol=1e-4)
+        out16 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        k.linear_tc(a, w, out16)
+        assert torch.equal(out16, out.bfloat16())          # same sums, rounded once
+    for m, n, kk in ((1, 96, 64), (8, 2048, 2048), (5, 203, 1032), (17, 203, 1032), (64, 8192, 2048), (33, 1024, 4096)):
+        a, w = rand((m, kk), torch.bfloat16, 150 + m, 0.5), rand((2 * n, kk), torch.bfloat16, 151 + m, 0.3)
+        both = torch.empty((m, 2 * n), dtype=torch.bfloat16, device="cuda")
+        k.linear_tc(a, w, both)
+        two_steps = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        k.swiglu(both, two_steps)
+        fused = torch.full((m, n + 5), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :n]
+        k.linear_tc_glu(a, w, fused)
+        assert torch.equal(fused, two_steps)
+    for m, nq, nkv, d, kk, ps in ((1, 4, 2, 32, 64, 4), (8, 32, 32, 64, 2048, 16), (5, 9, 3, 64, 264, 8), (16, 6, 1, 128, 1032, 16),
+                                  (64, 32, 32, 64, 2048, 16), (37, 15, 5, 64, 960, 16)):
+        width = (nq + 2 * nkv) * d
+        a, w = rand((m, kk), torch.bfloat16, 160 + m, 0.5), rand((width, kk), torch.bfloat16, 161 + m, 0.3)
+        inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))).cuda()
+        positions = torch.tensor([3 + 977 * i for i in range(m)], dtype=torch.int32).cuda()
+        n_pages = m + 2
+        slots = torch.tensor([((i * 5 + 1) % n_pages) * ps + (i * 3) % ps for i in range(m)], dtype=torch.int32)
+        if m > 2:
+            slots[2] = -1
+        slots = slots.cuda()
+        results = []
+        for fused in (False, True):
+            kp = torch.full((n_pages, nkv, ps, d), 7.0, dtype=torch.bfloat16, device="cuda")
+            vp = torch.full_like(kp, 7.0)
+            qkv = torch.zeros((m, width), dtype=torch.bfloat16, device="cuda")
+            if fused:
+                k.linear_tc_rope_store(a, w, qkv, positions, inv_freq, nq, nkv, d, slots, kp, vp, ps)
+            else:
+                k.linear_tc(a, w, qkv)
+                k.rope_cache_write(qkv, positions, inv_freq, nq, nkv, d, d, slots=slots, k_pages=kp, v_pages=vp, page_size=ps)
+            results.append((qkv[:, : nq * d].clone(), kp, vp))
+        for two, one in zip(*results):
+            assert torch.equal(two, one)
+    for n, kk in ((6144, 2048), (2048, 8192), (49155, 2048)):
+        a, w = rand((64, kk), torch.bfloat16, 170, 0.5), rand((n, kk), torch.bfloat16, 171, 0.5)
+        full = torch.empty((64, n), dtype=torch.float32, device="cuda")
+        k.linear_tc(a, w, full)
+        for m in (1, 8, 17, 40):
+            part = torch.empty((m, n), dtype=torch.float32, device="cuda")
+            k.linear_tc(a[:m], w, part)
+            assert torch.equal(part, full[:m]), (n, kk, m)
+    # the dispatcher: 17 to 64 rows of a product with many rows of w (an output head) take this kernel
+    a, w = rand((40, 256), torch.bfloat16, 172, 0.5), rand((49155, 256), torch.bfloat16, 173, 0.5)
+    out = torch.empty((40, 49155), dtype=torch.float32, device="cuda")
+    before = dict(k.launch_counts)
+    k.linear(a, w, out)
+    assert k.launch_counts["own"] == before["own"] + 1 and k.launch_counts["library"] == before["library"]
+    torch.testing.assert_close(out.double(), a.double() @ w.double().T, atol=2e-3, rtol=1e-4)
+
+
+def test_few_rows_give_a_row_the_same_bits_in_any_batch(k):
+    """The register-fed kernels (up to 16 rows): a row's sums do not depend on how many rows there are,
+    whichever variant (8, 16 or twice 16 warps per tile of w) the sizes of w select."""
+    for n, kk in ((6144, 2048), (2048, 2048), (2048, 8192), (49155 // 3, 2048), (960, 2560)):
+        a, w = rand((16, kk), torch.bfloat16, 180, 0.5), rand((n, kk), torch.bfloat16, 181, 0.5)
+        full = torch.empty((16, n), dtype=torch.float32, device="cuda")
+        k.linear_few_rows(a, w, full)
+        torch.testing.assert_close(full.double(), a.double() @ w.double().T, atol=2e-3 * (kk ** 0.5) / 8, rtol=1e-4)
+        for m in (1, 5, 8, 9):
+            part = torch.empty((m, n), dtype=torch.float32, device="cuda")
+            k.linear_few_rows(a[:m], w, part)
+            assert torch.equal(part, full[:m]), (n, kk, m)
 
 
 # --- attention -------------------------------------------------------------------------------

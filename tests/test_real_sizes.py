@@ -219,3 +219,48 @@ def test_cuttings_agree_with_each_other_at_real_layer_sizes_bf16(tmp_path):
         assert stats["mean_fraction"] <= helpers.BF16_AGREE_MEAN_FRACTION, stats
     finally:
         shutil.rmtree(tmp_path, ignore_errors=True)
+
+
+@pytest.mark.parametrize("which", ["2b", "500m"])
+def test_a_request_decodes_to_the_same_bits_whatever_shares_its_step(which, tmp_path):
+    """Requests with the same prompt (each prefilled alone, so their caches hold the same bits in different
+    pages) decode the same token: one alone, one beside 7 others, one beside 15.  The logits are equal bit
+    for bit: up to 16 rows the products of a decode step add a row's terms in an order that does not depend
+    on the number of rows, the norms and the rotary epilogue work row by row, and with contexts below the
+    smallest split every sequence is one split of the attention kernel.  Beside 31 and 63 others the
+    layers' products are the library's (whose sums depend on the number of rows): there the logits agree
+    within the band of two cuttings of a request."""
+    import shutil
+
+    from edgerag_b200 import Engine
+    from edgerag_b200.engine.step import StepEntry
+
+    folder = folder_for(tmp_path, which, "bfloat16")
+    try:
+        cfg = plain.read_config(folder)
+        engine = Engine.from_pretrained(folder, dtype="bfloat16", block_size=16, num_blocks=70 * 8, max_batch_size=70,
+                                        max_step_tokens=256, cuda_graphs=False)
+        runner = engine.runner
+        same = helpers.random_sequence(cfg["vocab"], 90, 5)
+        twins = [f"x{i}" for i in range(5)]
+        others = [f"o{i}" for i in range(63)]
+        for i, rid in enumerate(twins + others):
+            runner.admit(rid)
+            prompt = same if rid in twins else helpers.random_sequence(cfg["vocab"], 40 + (7 * i) % 70, 100 + i)
+            runner.step([StepEntry(rid, tokens=prompt)])
+        rows = {}
+        for twin, beside in zip(twins, (0, 7, 15, 31, 63)):
+            entries = [StepEntry(o, tokens=[11 + n]) for n, o in enumerate(others[:beside])]
+            entries.insert(beside // 2, StepEntry(twin, tokens=[321], want=[0]))       # somewhere in the middle of the batch
+            rows[beside] = runner.step(entries)[0].clone()
+        torch.cuda.synchronize()
+        assert torch.isfinite(rows[0]).all()
+        for beside in (7, 15):
+            differ = int((rows[beside] != rows[0]).sum())
+            assert differ == 0, f"beside {beside} others: {differ} of {rows[0].numel()} logits differ"
+        scale = float(rows[0].abs().max())
+        for beside in (31, 63):
+            diff = (rows[beside] - rows[0]).abs()
+            assert float(diff.max()) <= helpers.BF16_AGREE_FRACTION * scale and float(diff.mean()) <= helpers.BF16_AGREE_MEAN_FRACTION * scale
+    finally:
+        shutil.rmtree(tmp_path, ignore_errors=True)
