@@ -316,22 +316,30 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
     for (int t = 0; t < NT; ++t) {
       const bool live = tile < n_tiles && t * 8 < M;       // (the same for the whole cluster)
       if (CL == 1 && !live) continue;
-      __syncthreads();
+      if (rt + t > 0) __syncthreads();                   // (the sums of the round before have been read)
 #pragma unroll
       for (int i = 0; i < 4; ++i) red[warp][lane][i] = acc[t][rt][i];
       __syncthreads();
       const int idx = threadIdx.x;
       if (idx < kFinishers && live) {
         float v0 = 0.f, v1 = 0.f;
+        // (32 warps: the sums of the first and of the second 16 are added last, as two blocks of a cluster would)
+        constexpr int kHalf = kSkWarps == 32 ? 16 : kSkWarps;
+        float u0 = 0.f, u1 = 0.f;
         if constexpr (PAIRED) {
           const int l = idx / 2, i = idx % 2;
 #pragma unroll
-          for (int wv = 0; wv < kSkWarps; ++wv) { v0 += red[wv][l][i]; v1 += red[wv][l][i + 2]; }
+          for (int wv = 0; wv < kHalf; ++wv) { v0 += red[wv][l][i]; v1 += red[wv][l][i + 2]; }
+#pragma unroll
+          for (int wv = kHalf; wv < kSkWarps; ++wv) { u0 += red[wv][l][i]; u1 += red[wv][l][i + 2]; }
         } else {
           const int l = idx / 4, i = idx % 4;
 #pragma unroll
-          for (int wv = 0; wv < kSkWarps; ++wv) v0 += red[wv][l][i];
+          for (int wv = 0; wv < kHalf; ++wv) v0 += red[wv][l][i];
+#pragma unroll
+          for (int wv = kHalf; wv < kSkWarps; ++wv) u0 += red[wv][l][i];
         }
+        if constexpr (kSkWarps == 32) { v0 += u0; v1 += u1; }
         if constexpr (CL == 1) {
           finish(tile, t, idx, v0, v1);
         } else {
@@ -403,8 +411,13 @@ int launch_skinny_tiles(const __nv_bfloat16* ap, const __nv_bfloat16* wp, void* 
   const int n_tiles = MODE == 2 ? (N + 7) / 8 : (N + 15) / 16;
   const unsigned blocks = (unsigned)((n_tiles + RT - 1) / RT);
   const unsigned sms = (unsigned)sm_count();
-  if ((unsigned)n_tiles <= sms && K >= 4096)
-    launch_skinny(linear_skinny_kernel<NT, RT, MODE, 16, 2>, dim3(2 * blocks), dim3(512), 0, 2, s, ap, wp, out, M, N, K, lda, ldw, ldo, n_tiles, ra);
+  if ((unsigned)n_tiles <= sms && K >= 4096) {
+    // 32 warps: one block where its registers allow (up to 16 rows of a), else two blocks of 16 on two SMs
+    if constexpr (NT * RT <= 2)
+      launch_skinny(linear_skinny_kernel<NT, RT, MODE, 32, 1>, dim3(blocks), dim3(1024), 0, 1, s, ap, wp, out, M, N, K, lda, ldw, ldo, n_tiles, ra);
+    else
+      launch_skinny(linear_skinny_kernel<NT, RT, MODE, 16, 2>, dim3(2 * blocks), dim3(512), 0, 2, s, ap, wp, out, M, N, K, lda, ldw, ldo, n_tiles, ra);
+  }
   else if ((unsigned)n_tiles < 2 * sms && K >= 1024)
     launch_skinny(linear_skinny_kernel<NT, RT, MODE, 16, 1>, dim3(blocks), dim3(512), 0, 1, s, ap, wp, out, M, N, K, lda, ldw, ldo, n_tiles, ra);
   else
