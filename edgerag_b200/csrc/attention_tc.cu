@@ -49,6 +49,73 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
   }
 }
 
+constexpr int kCombineMaxSplits = 64;     // splits of one sequence that a merge takes
+constexpr int kMergeWarps = 9;            // warps of the largest block that merges (eight and a copy warp)
+
+// The merge of a (sequence, head group)'s splits by the block that finishes last among them, in place
+// of a second kernel.  Every block adds one to the group's counter after its partial results are
+// visible device-wide; the block that sees n_splits - 1 there is the last, puts the counter back to
+// zero (so the array stays zero between launches) and merges: per query head the weights of the
+// splits from their maxima (log2 domain), then every output element as a sum over the splits in
+// their order.  The result therefore does not depend on which block came last.  A block that gave
+// up on a wait does not count, so after a flagged status the host zeroes the counters.
+template <int D>
+__device__ __forceinline__ void merge_splits_if_last(int* counter, const float* part_acc, const float* part_ml,
+                                                     size_t head0, int n_heads, int n_splits, int max_splits,
+                                                     __nv_bfloat16* o) {
+  __shared__ int s_last;
+  __shared__ float s_w[kMergeWarps][kCombineMaxSplits];     // the splits' weights, per warp
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int last = atomicAdd(counter, 1) == n_splits - 1;
+    if (last) atomicExch(counter, 0);
+    s_last = last;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  if (warp >= kMergeWarps) return;
+  float* w = s_w[warp];
+  for (int h = warp; h < n_heads; h += min(n_warps, kMergeWarps)) {
+    const size_t base = (head0 + h) * max_splits;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    if (lane < n_splits) { m0 = __ldcg(part_ml + (base + lane) * 2); l0 = __ldcg(part_ml + (base + lane) * 2 + 1); }
+    if (lane + 32 < n_splits) { m1 = __ldcg(part_ml + (base + lane + 32) * 2); l1 = __ldcg(part_ml + (base + lane + 32) * 2 + 1); }
+    const float m = warp_max(fmaxf(m0, m1));
+    const float w0 = lane < n_splits ? exp2f(m0 - m) : 0.f, w1 = lane + 32 < n_splits ? exp2f(m1 - m) : 0.f;
+    w[lane] = w0;
+    w[lane + 32] = w1;
+    const float inv = 1.f / warp_sum(l0 * w0 + l1 * w1);
+    __syncwarp();
+    // A lane owns D / 32 neighbouring elements, so that a split costs it one load and many are in flight.
+    constexpr int V = D / 32;
+    float sum[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) sum[i] = 0.f;
+    const float* src = part_acc + base * D + lane * V;
+#pragma unroll 8
+    for (int sp = 0; sp < n_splits; ++sp) {
+      float x[V];
+      if constexpr (V == 4) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * D));
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+      } else if constexpr (V == 2) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(src + (size_t)sp * D));
+        x[0] = v.x; x[1] = v.y;
+      } else {
+        x[0] = __ldcg(src + (size_t)sp * D);
+      }
+#pragma unroll
+      for (int i = 0; i < V; ++i) sum[i] += x[i] * w[sp];
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) o[(size_t)h * D + lane * V + i] = __float2bfloat16_rn(sum[i] * inv);
+    __syncwarp();
+  }
+}
+
 template <int D, int R>   // head size; query heads per kv head (1..kMaxGroup)
 __global__ void __launch_bounds__(kDecThreads)
 attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
@@ -57,7 +124,8 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
                              const int* __restrict__ token_of_seq, const int* __restrict__ positions,
                              float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
                              int nkv, int page_size, int split_keys, float scale_log2, int hg,
-                             __nv_bfloat16* __restrict__ out, int out_row_stride, int* __restrict__ status) {
+                             __nv_bfloat16* __restrict__ out, int out_row_stride, int* __restrict__ status,
+                             int* __restrict__ counters) {
   // Everything up to chain_wait() below reads only what earlier steps or the host wrote (the batch's
   // metadata, keys and values of earlier tokens), so it runs while the kernel before this one (the
   // one that rotates q and writes this step's keys and values) is still at work.
@@ -299,12 +367,15 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
     part_acc[slot * D + d] = sum;
     if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
   }
+  if (max_splits > 1 && counters)
+    merge_splits_if_last<D>(counters + (size_t)seq * gridDim.y + blockIdx.y, part_acc, part_ml,
+                            (size_t)seq * nq + (size_t)kvh0 * R, hg_here * R, min(pos / split_keys + 1, max_splits), max_splits,
+                            out + (size_t)t * out_row_stride + (size_t)kvh0 * R * D);
 }
 
 // Merges the splits of each (sequence, head).  The partial maxima are in the log2 domain.  The
 // weights of the splits are computed by the first lanes in parallel; every output element is then
 // a sum over the splits in their order.
-constexpr int kCombineMaxSplits = 64;
 __global__ void __launch_bounds__(64)
 attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                      const int* __restrict__ token_of_seq, const int* __restrict__ positions,
@@ -344,9 +415,14 @@ attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const f
 // does not divide gets one block for all its heads when they are at most 8 and their copy stays
 // within 16 KB (5 heads of 64 with 16-token pages: 10 KB copies instead of 2 KB ones), else a last
 // group with the heads that are left.
-int decode_head_group(int nkv, int head_dim, int page_size, int split_keys) {
+// `want` > 0 asks for that many heads per block (a power of two that passes the same checks; 1 always
+// does): fewer heads per block give more and shorter blocks, which is what a small batch of short
+// contexts needs.  The answer is 0 when `want` cannot be had.
+int decode_head_group(int nkv, int head_dim, int page_size, int split_keys, int want = 0) {
   const int stage_rows = kDecWarps * (32 / (head_dim / 8)) * kKeysPerGroup;
   auto fits = [&](int hg) { return hg <= kDecWarps && (stage_rows / hg) % page_size == 0 && stage_rows / hg >= page_size; };
+  if (want == 1) return 1;
+  if (want > 1) return (want & (want - 1)) == 0 && split_keys % page_size == 0 && fits(want) && want < 2 * nkv ? want : 0;
   if (split_keys % page_size) return 1;
   int hg = 1;
   while (hg * 2 * page_size * head_dim * 2 <= 8192 && fits(hg * 2) && hg < nkv) hg *= 2;
@@ -362,8 +438,10 @@ template <int D, int R>
 int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                        const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                        float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
-                       int split_keys, float scale_log2, void* out, int out_row_stride, int* status, cudaStream_t s) {
-  const int hg = decode_head_group(nkv, D, page_size, split_keys);
+                       int split_keys, float scale_log2, void* out, int out_row_stride, int* status, int* counters, int head_group,
+                       cudaStream_t s) {
+  const int hg = decode_head_group(nkv, D, page_size, split_keys, head_group);
+  if (hg <= 0) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: %d heads per block with pages of %d and splits of %d", head_group, page_size, split_keys);
   constexpr int STAGE_BYTES = kDecWarps * (32 / (D / 8)) * kKeysPerGroup * D * 2;
   const size_t smem = 2 * kStages * STAGE_BYTES + 64 + (size_t)kDecWarps * R * (D + 2) * sizeof(float) + 128 +
                       (size_t)(split_keys / page_size + 2) * sizeof(int);
@@ -377,7 +455,7 @@ int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, con
   }
   launch_chained(kern, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kDecThreads), smem, s, (const __nv_bfloat16*)q, q_row_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, token_of_seq, positions,
-      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, (__nv_bfloat16*)out, out_row_stride, status);
+      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, (__nv_bfloat16*)out, out_row_stride, status, counters);
   return check_launch("attention_decode_bulk");
 }
 
@@ -385,12 +463,13 @@ template <int D>
 int dispatch_group(int r, const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                    const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                    float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
-                   int split_keys, float scale_log2, void* out, int out_row_stride, int* status, cudaStream_t s) {
+                   int split_keys, float scale_log2, void* out, int out_row_stride, int* status, int* counters, int head_group,
+                   cudaStream_t s) {
 #define ERB_R(RR)                                                                                              \
   case RR: return launch_decode_bulk<D, RR>(q, q_row_stride, k_pages, v_pages, block_tables, max_pages,        \
                                             token_of_seq, positions, part_acc, part_ml, max_splits, n_seqs, nq, \
                                             nkv, page_size, split_keys, scale_log2, out, out_row_stride,       \
-                                            status, s);
+                                            status, counters, head_group, s);
   switch (r) { ERB_R(1) ERB_R(2) ERB_R(3) ERB_R(4) ERB_R(5) ERB_R(6) ERB_R(7) ERB_R(8) }
 #undef ERB_R
   return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: %d query heads per kv head (at most %d)", r, kMaxGroup);
@@ -454,7 +533,8 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ token_of_seq, const int* __restrict__ positions,
                             float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
                             int nkv, int page_size, int split_keys, float scale_log2, int hg,
-                            __nv_bfloat16* __restrict__ out, int out_row_stride, int* __restrict__ status) {
+                            __nv_bfloat16* __restrict__ out, int out_row_stride, int* __restrict__ status,
+                            int* __restrict__ counters) {
   constexpr int D = 64;
   const int R = nq / nkv;
   extern __shared__ uint8_t smem_raw[];
@@ -676,6 +756,10 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     part_acc[slot * D + d] = sum;
     if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
   }
+  if (max_splits > 1 && counters)
+    merge_splits_if_last<D>(counters + (size_t)seq * gridDim.y + blockIdx.y, part_acc, part_ml,
+                            (size_t)seq * nq + (size_t)kvh0 * R, hg_here * R, min(pos / split_keys + 1, max_splits), max_splits,
+                            out + (size_t)t * out_row_stride + (size_t)kvh0 * R * D);
 }
 
 }  // namespace
@@ -696,7 +780,7 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
                                         const int* token_of_seq, const int* positions, void* out, int out_row_stride,
                                         float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv,
                                         int head_dim, int page_size, int split_keys, float scale, int* status,
-                                        void* stream) {
+                                        int* counters, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
   if (!erb_attention_decode_gqa_supported(nq, nkv, head_dim, page_size, split_keys))
     return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: %d/%d heads of %d, pages of %d, splits of %d", nq, nkv,
@@ -733,8 +817,9 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
   launch_chained(attention_decode_gqa_kernel, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kGqaThreads), smem, s,
                  mk, mv, mkl, mvl, (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, token_of_seq, positions,
                  part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, (__nv_bfloat16*)out, out_row_stride,
-                 status);
-  if ((rc = check_launch("attention_decode_gqa")) || max_splits == 1) return rc;      // a single split wrote the result itself
+                 status, counters);
+  // a single split wrote the result itself; with counters the block that finishes last merges the splits
+  if ((rc = check_launch("attention_decode_gqa")) || max_splits == 1 || counters) return rc;
   launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
       (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
   return check_launch("attention_decode_bulk_combine");
@@ -747,6 +832,13 @@ ERB_EXPORT int erb_attention_decode_bulk_groups(int nkv, int head_dim, int page_
   return (nkv + hg - 1) / hg;
 }
 
+// Heads per block that erb_attention_decode_bulk uses when asked for `want` (0: its own choice); 0 when
+// `want` cannot be had with these sizes.
+ERB_EXPORT int erb_attention_decode_bulk_head_group(int nkv, int head_dim, int page_size, int split_keys, int want) {
+  if (nkv <= 0 || page_size <= 0 || split_keys <= 0 || (head_dim != 32 && head_dim != 64 && head_dim != 128)) return 0;
+  return decode_head_group(nkv, head_dim, page_size, split_keys, want);
+}
+
 // Same contract as the general decode entry point (scratch provided by the caller, splits at
 // absolute multiples of split_keys), for bfloat16 with head_dim 32 / 64 / 128, no window, at most
 // 8 query heads per kv head, and page rows that are 16-byte multiples.
@@ -754,7 +846,8 @@ ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const 
                                          const int* block_tables, int max_pages, const int* token_of_seq,
                                          const int* positions, void* out, int out_row_stride, float* part_acc,
                                          float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int head_dim,
-                                         int page_size, int split_keys, float scale, int* status, void* stream) {
+                                         int page_size, int split_keys, float scale, int* status, int* counters,
+                                         int head_group, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
   if (nq <= 0 || nkv <= 0 || nq % nkv) return fail(ERB_ERR_ARG, "attention_decode_bulk: bad head counts");
   if (max_splits <= 0 || split_keys <= 0 || !part_acc || !part_ml || !status || page_size <= 0)
@@ -771,16 +864,17 @@ ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const 
   switch (head_dim) {
     case 32: rc = dispatch_group<32>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                      positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size, split_keys,
-                                     scale_log2, out, out_row_stride, status, s); break;
+                                     scale_log2, out, out_row_stride, status, counters, head_group, s); break;
     case 64: rc = dispatch_group<64>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                      positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size, split_keys,
-                                     scale_log2, out, out_row_stride, status, s); break;
+                                     scale_log2, out, out_row_stride, status, counters, head_group, s); break;
     case 128: rc = dispatch_group<128>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                        positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size,
-                                       split_keys, scale_log2, out, out_row_stride, status, s); break;
+                                       split_keys, scale_log2, out, out_row_stride, status, counters, head_group, s); break;
     default: return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: head_dim %d (takes 32, 64, 128)", head_dim);
   }
-  if (rc || max_splits == 1) return rc;      // a single split wrote the result itself
+  // a single split wrote the result itself; with counters the block that finishes last merges the splits
+  if (rc || max_splits == 1 || counters) return rc;
   launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
       (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
   return check_launch("attention_decode_bulk_combine");

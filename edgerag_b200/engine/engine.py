@@ -83,6 +83,11 @@ class EngineOptions:
     #: back on the device); what ``step`` returns is then one step behind what the GPU is running
     lookahead: bool = True
     poison_freed_pages: bool = False    # tests: NaN in free pages, so a stale read shows
+    #: launch shapes that do not depend on the batch (decode attention always in splits of 512 keys with
+    #: the default grouping of heads): up to 16 single-token rows a request's logits are then the same
+    #: bits whatever shares its step; off, the attention kernel's shape follows the batch, which is
+    #: faster for small batches and short contexts
+    batch_invariant: bool = False
 
 
 @dataclass
@@ -135,7 +140,7 @@ class Engine:
         self.pools = DevicePools(layout, options.block_size, n_pages, options.max_batch_size, self.dtype,
                                  self.device, poison=options.poison_freed_pages)
         self.runner = ModelRunner(model, self.cache, self.pools, max_step_tokens=max_step,
-                                  cuda_graphs=options.cuda_graphs)
+                                  cuda_graphs=options.cuda_graphs, batch_invariant=options.batch_invariant)
         self.scheduler = Scheduler(self.cache, SchedulerConfig(
             max_batch_size=options.max_batch_size, prefill_chunk_size=options.chunk_size,
             max_prefills_per_step=options.max_prefills_per_step, max_step_tokens=max_step,

@@ -91,12 +91,16 @@ class StepContext:
         self._runner = runner
         self.page_size = runner.cache.page_size
         self.dtype = runner.dtype
+        #: parts choose launch shapes that do not depend on the batch (a request's results are then the
+        #: same bits whatever shares its step, at some cost in speed)
+        self.batch_invariant = runner.batch_invariant
         self.status = runner.status
         self.n_tokens = self.n_seqs = self.n_decode = self.n_wanted = self.n_fed_back = 0
         self.token_ids = self.embed_row = self.positions = self.seq_of_token = None
         self.token_of_seq = self.want_rows = self.state_slots = self.seq_starts = None
         self.embeds: torch.Tensor | None = None
         self.max_pages = 1
+        self.bound_pages, self.granule_pages = 4, 1
         self.graph_key: tuple | None = None          # set when the step has the fixed layout of a CUDA graph
         self.slots: list[torch.Tensor] = []
         self.block_tables: list[torch.Tensor] = []
@@ -119,13 +123,18 @@ class StepContext:
         return self._runner.pools.states[f"{name}@{cache_layer}"]
 
     def max_keys_bound(self) -> int:
-        """A power-of-two bound (in pages) on the longest context of the batch, times the page size."""
-        return max(4, 1 << (self.max_pages - 1).bit_length()) * self.page_size
+        """A bound on the longest context of the batch that steps of one captured layout share: its pages
+        rounded up to a quarter of their power-of-two bucket (``kernels.context_bound``), in tokens."""
+        return self.bound_pages * self.page_size
+
+    def keys_granule(self) -> int:
+        """The step of ``max_keys_bound`` in tokens: the batch's longest context lies within one granule below the bound."""
+        return self.granule_pages * self.page_size
 
     def decode_splits(self, window: int, split_keys: int = kernels.DECODE_SPLIT_KEYS) -> int:
         """Largest number of key splits any single-token sequence of the batch has."""
         if self.graph_key is not None:   # a captured layout: the bound must hold for every replay
-            bound = -(-(self.max_pages * self.page_size) // split_keys)
+            bound = -(-(self.bound_pages * self.page_size) // split_keys)
             return bound if window <= 0 else min(bound, window // split_keys + 2)
         most = 1
         for pos in self.host_positions_last[: self.n_decode]:
@@ -138,8 +147,9 @@ class ModelRunner:
     """Owns the model, the cache and the scratch of one device, and runs steps on them."""
 
     def __init__(self, model, cache: CacheManager, pools: DevicePools, max_step_tokens: int,
-                 check_status: bool = False, cuda_graphs: bool = False) -> None:
+                 check_status: bool = False, cuda_graphs: bool = False, batch_invariant: bool = False) -> None:
         self.model = model
+        self.batch_invariant = bool(batch_invariant)
         self.cache = cache
         self.pools = pools
         self.device = pools.device
@@ -257,6 +267,7 @@ class ModelRunner:
         # A step whose layout is fully described by a small key can be replayed from a CUDA graph:
         # single tokens, and portions of prompts given as ids (their lengths are part of the key).
         graphable = self.graphs_enabled and all(e.embeds is None for e in ordered)
+        bound_pages, granule_pages = kernels.context_bound(max_pages)
         if graphable:
             # a captured step has a fixed layout: block tables padded to a power of two of pages
             max_pages = max(4, 1 << (max_pages - 1).bit_length())
@@ -310,9 +321,10 @@ class ModelRunner:
         ctx.block_tables = [tables_d[g * per: (g + 1) * per].view(n_seqs, max_pages) for g in range(n_groups)]
         ctx.n_tokens, ctx.n_seqs, ctx.n_decode, ctx.n_wanted = total, n_seqs, n_decode, int(want_rows.size)
         ctx.max_pages = max_pages
+        ctx.bound_pages, ctx.granule_pages = bound_pages, granule_pages
         ctx.n_fed_back = sum(1 for e in ordered if e.fed_back is not None)
         if graphable:
-            ctx.graph_key = (n_decode, tuple(e.n_tokens for e in ordered[n_decode:]), max_pages, int(want_rows.size))
+            ctx.graph_key = (n_decode, tuple(e.n_tokens for e in ordered[n_decode:]), max_pages, bound_pages, int(want_rows.size))
         if embed_chunks:
             ctx.embeds = torch.cat([c.to(device=self.device, dtype=self.dtype, non_blocking=True)
                                     for c in embed_chunks], dim=0).contiguous()
@@ -355,6 +367,7 @@ class ModelRunner:
             torch.cuda.current_stream().synchronize()
             self.status.zero_()
             self._status_host.zero_()
+            kernels.reset_split_counters()      # a block that gave up did not count itself among its sequence's splits
             if code >= 1000000:
                 raise StepError(f"an attention kernel gave up (code {code}: 1xxxxxx prefill wait, 2xxxxxx decode "
                                 "wait, 3000000 shared-memory alignment, 4xxxxxx a wait of a product for few rows); "

@@ -53,10 +53,10 @@ _SIGNATURES = {
                                  c_void_p],
     "erb_attention_decode_bulk": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_float, c_void_p, c_void_p],
+                                  c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
     "erb_attention_decode_gqa": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_float, c_void_p, c_void_p],
+                                 c_float, c_void_p, c_void_p, c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
@@ -64,7 +64,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 2, "erb_attention_decode_gqa": 2, "erb_linear": 0}
+_LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
 TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
 
@@ -491,6 +491,66 @@ def _choose_decode_split(device: int, n_seqs: int, n_kv_heads: int, max_keys: in
     return fits[-1] if blocks[fits[-1]] < slots else min(fits, key=lambda s: abs(blocks[s] - slots))
 
 
+def context_bound(pages: int) -> tuple[int, int]:
+    """(bound, granule) in pages for a batch whose longest context has ``pages`` pages: the bound is
+    ``pages`` rounded up to a multiple of the granule, a quarter of the power-of-two bucket it lies in
+    (at least 4 pages).  Steps that share a bound share launch shapes (and a captured graph); the
+    longest context then lies within one granule below the bound."""
+    bucket = max(4, 1 << (max(1, pages) - 1).bit_length())
+    granule = max(1, bucket // 4)
+    return -(-max(1, pages) // granule) * granule, granule
+
+
+def choose_decode_plan(n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int, head_dim: int = 64,
+                       grouped: bool = False, granule: int = 0) -> tuple[int, int]:
+    """(keys per split, kv heads per block) for a decode step whose longest context lies in
+    (``max_keys`` - ``granule``, ``max_keys``]; heads per block 0 means the kernel's own choice.
+    ``grouped``: the kernel for several query heads per kv head runs, which groups by itself."""
+    if grouped or head_dim not in (32, 64, 128):
+        return choose_decode_split(n_seqs, n_kv_heads, max_keys, page_size, head_dim), 0
+    return _choose_decode_plan(torch._C._cuda_getDevice(), n_seqs, n_kv_heads, max_keys, page_size, head_dim,
+                               granule if granule > 0 else max_keys)
+
+
+@functools.lru_cache(maxsize=4096)
+def _choose_decode_plan(device: int, n_seqs: int, n_kv_heads: int, max_keys: int, page_size: int, head_dim: int,
+                        granule: int) -> tuple[int, int]:
+    """The bulk kernel runs one block per (sequence, group of kv heads, split), two blocks per SM.  By
+    default it groups as many neighbouring heads as make a page's copy about 8 KB, which long contexts
+    and large batches need for bandwidth; a small batch or a short context then gives far fewer blocks
+    than SMs, each walking through many stages one after the other.  Measured with caches read from
+    DRAM (batches of 1 to 64, contexts of 640 to 8,192): best is the plan with the fewest heads per
+    block (from 2) and then the longest splits whose blocks fill most of one wave, e.g. 16 sequences
+    of 640 tokens 15 us with 2 heads per block and no split against 23 us with 8 heads and splits of
+    256; where no such plan exists the rule of ``_choose_decode_split`` with the default grouping
+    stands (it is as good for 8 sequences of 8,192 tokens and better beyond).  Splits are either at
+    most a granule long or hold the whole context: a split between the two leaves the longest
+    context with one full split and a short rest, and the step waits for the full one (8 sequences
+    of 640 tokens: 1.53 ms a step with splits of 512, 1.46 ms with splits of 256).  A function of the
+    batch's size and of the bound on the longest context only."""
+    split = _choose_decode_split(device, n_seqs, n_kv_heads, max_keys, page_size, head_dim)
+    lib = native.load("attention_tc", None)
+    default = lib.erb_attention_decode_bulk_head_group(n_kv_heads, head_dim, page_size, 512, 0)
+    slots = 2 * _sm_counts[device]
+    sizes = [s for s in (2048, 1024, 512, 256, 128, 64)
+             if s % page_size == 0 and -(-max_keys // s) <= 64 and (s <= granule or s >= max_keys)]
+    finest = None
+    for hg in (2, 4, 8):
+        if hg > default:
+            break
+        for s in sizes:
+            if lib.erb_attention_decode_bulk_head_group(n_kv_heads, head_dim, page_size, s, hg) != hg:
+                continue
+            blocks = n_seqs * -(-n_kv_heads // hg) * -(-max_keys // s)
+            if 0.6 * slots <= blocks <= slots:
+                return s, hg
+            if hg == 2:
+                finest = (s, hg, blocks)
+    if finest is not None and finest[2] < 0.6 * slots:       # even the finest plan leaves SMs idle: take it
+        return finest[0], finest[1]
+    return split, 0
+
+
 def decode_scratch_floats(n_seqs: int, n_q_heads: int, head_dim: int, max_splits: int) -> tuple[int, int]:
     return n_seqs * n_q_heads * max_splits * head_dim, n_seqs * n_q_heads * max_splits * 2
 
@@ -529,11 +589,37 @@ def decode_bulk_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_he
             and n_q_heads // n_kv_heads <= 8 and max_splits <= 64)
 
 
+_split_counters: dict[torch.device, torch.Tensor] = {}
+
+
+def split_counters(device: torch.device, n: int) -> torch.Tensor:
+    """The counters by which the split decode kernels find the block that finishes last for each
+    (sequence, group of kv heads): one zeroed int32 array per device, shared by all calls (calls on
+    one stream follow each other; the kernels leave every counter at zero).  It keeps its address, so
+    that captured graphs stay valid."""
+    buf = _split_counters.get(device)
+    if buf is None:
+        buf = _split_counters[device] = torch.zeros(1 << 18, dtype=torch.int32, device=device)
+    if n > buf.numel():
+        raise KernelError(f"decode attention: {n} (sequence, head group) pairs, at most {buf.numel()}")
+    return buf
+
+
+def reset_split_counters() -> None:
+    """Zeroes the counters again: needed after a kernel gave up on a wait (a flagged status), since
+    its block did not count."""
+    for buf in _split_counters.values():
+        buf.zero_()
+
+
 def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                           token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
                           scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
-                          status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS) -> None:
-    """``attention_decode`` for bfloat16 with keys and values streamed by bulk asynchronous copies."""
+                          status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS, head_group: int = 0) -> None:
+    """``attention_decode`` for bfloat16 with keys and values streamed by bulk asynchronous copies.
+    The splits of a sequence are merged by the block that finishes last (``split_counters``), so
+    this is one launch.  ``head_group``: kv heads per block (a power of two; 0: as many as make a
+    page's copy about 8 KB)."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pages, "k_pages", torch.bfloat16)
     _need(v_pages, "v_pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
     _need(token_of_seq, "token_of_seq", torch.int32); _need(positions, "positions", torch.int32)
@@ -549,9 +635,8 @@ def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
     _call(_fn("attention_tc", None, "erb_attention_decode_bulk"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
-          n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(), _stream())
-    if max_splits == 1:
-        launch_counts["own"] -= 1       # a single split writes the result itself: no second kernel
+          n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(),
+          split_counters(q.device, n_seqs * nkv).data_ptr(), int(head_group), _stream())
 
 
 @functools.lru_cache(maxsize=4096)
@@ -586,9 +671,8 @@ def attention_decode_gqa(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     _call(_fn("attention_tc", None, "erb_attention_decode_gqa"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
           v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
-          n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(), _stream())
-    if max_splits == 1:
-        launch_counts["own"] -= 1       # a single split writes the result itself: no second kernel
+          n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(),
+          split_counters(q.device, n_seqs * nkv).data_ptr(), _stream())
 
 
 #: query rows of one (sequence, head) that a block of the tensor-core prefill kernel takes

@@ -72,6 +72,7 @@ def _time(fn, iters: int, warmup: int, rounds: int = 5) -> float:
 
 
 def _paged(batch: int, context: int, nkv: int, d: int, page: int, dtype, shuffle: bool = True):
+    """Key and value pools of ``batch`` sequences of ``context`` tokens with their block tables."""
     pages_per = -(-context // page)
     n_pages = batch * pages_per
     kp = torch.randn((n_pages, nkv, page, d), device="cuda", dtype=torch.float32).to(dtype)
@@ -83,32 +84,44 @@ def _paged(batch: int, context: int, nkv: int, d: int, page: int, dtype, shuffle
 
 def decode_attention(a) -> dict:
     dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
-    kp, vp, tables = _paged(a.batch, a.context, a.kv_heads, a.head_dim, a.page, dtype, not a.sequential_pages)
+    nbytes = 2 * a.batch * a.context * a.kv_heads * a.head_dim * (2 if dtype == torch.bfloat16 else 4)
+    # --cold: rotate over so many caches that each launch finds its keys and values in DRAM, as a
+    # step does whose weights have passed through L2 since the layer's cache was last read
+    reps = max(2, int(300e6 // nbytes) + 1) if a.cold else 1
+    caches = [_paged(a.batch, a.context, a.kv_heads, a.head_dim, a.page, dtype, not a.sequential_pages) for _ in range(reps)]
+    state = {"i": 0}
+
+    def cache():
+        state["i"] = (state["i"] + 1) % reps
+        return caches[state["i"]]
+
     q = torch.randn((a.batch, a.heads * a.head_dim), device="cuda").to(dtype)
     out = torch.empty_like(q)
     pos = torch.full((a.batch,), a.context - 1, dtype=torch.int32, device="cuda")
     tok = torch.arange(a.batch, dtype=torch.int32, device="cuda")
     if a.split <= 0:        # as the engine chooses it: from the batch and a power-of-two bound on the context
-        a.split = kernels.choose_decode_split(a.batch, a.kv_heads, 1 << (a.context - 1).bit_length(), a.page, a.head_dim)
+        bound, granule = kernels.context_bound(-(-a.context // a.page))
+        a.split, heads = kernels.choose_decode_plan(a.batch, a.kv_heads, bound * a.page, a.page, a.head_dim, a.kernel != "bulk",
+                                                    granule * a.page)
+        a.head_group = a.head_group or heads
     splits = (a.context - 1) // a.split + 1
     acc_n, ml_n = kernels.decode_scratch_floats(a.batch, a.heads, a.head_dim, splits)
     acc, ml = torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     scale = a.head_dim ** -0.5
     if a.kernel == "gqa":
-        fn = lambda: kernels.attention_decode_gqa(q, kp, vp, tables, tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
+        fn = lambda: kernels.attention_decode_gqa(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
                                                   status, split_keys=a.split)
     elif a.kernel == "bulk":
-        fn = lambda: kernels.attention_decode_bulk(q, kp, vp, tables, tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
-                                                   status, split_keys=a.split)
+        fn = lambda: kernels.attention_decode_bulk(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
+                                                   status, split_keys=a.split, head_group=a.head_group)
     else:
-        fn = lambda: kernels.attention_decode(q, kp, vp, tables, tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
+        fn = lambda: kernels.attention_decode(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
                                               split_keys=a.split)
-    us = _time(fn, a.iters, a.warmup)
-    nbytes = 2 * a.batch * a.context * a.kv_heads * a.head_dim * kp.element_size()
-    return {"case": "decode-attention", "kernel": a.kernel, "split": a.split, "us": round(us, 2), "bytes": nbytes,
-            "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
-            "status": int(status), "larger_than_l2": nbytes > 126e6}
+    us = _time(fn, max(a.iters, 2 * reps), a.warmup)
+    return {"case": "decode-attention", "kernel": a.kernel, "split": a.split, "head_group": a.head_group, "us": round(us, 2),
+            "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
+            "status": int(status), "from_dram": bool(a.cold) or nbytes > 126e6}
 
 
 def prefill_attention(a) -> dict:
@@ -236,6 +249,8 @@ def main(argv=None) -> int:
     d.add_argument("--context", type=int, default=8192)
     d.add_argument("--split", type=int, default=0, help="keys per split; 0: the engine's choice for this batch")
     d.add_argument("--kernel", choices=["bulk", "gqa", "general"], default="bulk")
+    d.add_argument("--head-group", type=int, default=0, help="kv heads per block of the bulk kernel; 0: its own choice")
+    d.add_argument("--cold", action="store_true", help="rotate over several caches so that none is found in L2")
     p = sub.add_parser("prefill-attention", parents=[common, att])
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--past", type=int, default=0)

@@ -75,7 +75,14 @@ class Attention(Mixer):
         tables = ctx.block_tables[group]
         nd = ctx.n_decode
         if nd:
-            split = kernels.choose_decode_split(nd, self.n_kv, ctx.max_keys_bound(), ctx.page_size, d)
+            grouped = self.n_q != self.n_kv and kernels.decode_gqa_supported(self.dtype, d, self.window, self.n_q, self.n_kv,
+                                                                              ctx.page_size, kernels.DECODE_SPLIT_KEYS)
+            if ctx.batch_invariant:     # one plan for every batch: a sequence's sums are then added in one order
+                split, heads_per_block = kernels.DECODE_SPLIT_KEYS, 0
+            else:
+                split, heads_per_block = kernels.choose_decode_plan(nd, self.n_kv, ctx.max_keys_bound(), ctx.page_size, d,
+                                                                    grouped or self.window > 0 or self.dtype != torch.bfloat16,
+                                                                    ctx.keys_granule())
             max_splits = ctx.decode_splits(self.window, split)
             need_acc, need_ml = kernels.decode_scratch_floats(nd, self.n_q, d, max_splits)
             part_acc = ctx.buf("attn.part_acc", (need_acc,), torch.float32)
@@ -87,7 +94,7 @@ class Attention(Mixer):
             elif kernels.decode_bulk_supported(self.dtype, d, self.window, self.n_q, self.n_kv, max_splits):
                 kernels.attention_decode_bulk(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                               out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,
-                                              split_keys=split)
+                                              split_keys=split, head_group=heads_per_block)
             else:
                 kernels.attention_decode(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                          out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits,

@@ -452,6 +452,62 @@ def test_attention_decode_bulk_copies(k, nq, nkv, d, ps, split):
     torch.testing.assert_close(out.float().cpu(), want, **tol(dtype))
 
 
+@pytest.mark.parametrize("nq,nkv,d,ps,split,heads", [(8, 8, 64, 16, 64, 1), (8, 8, 64, 16, 64, 2), (8, 8, 64, 16, 128, 4),
+                                                     (32, 32, 64, 16, 256, 2), (12, 6, 64, 8, 128, 4), (7, 7, 32, 16, 64, 2),
+                                                     (5, 5, 128, 16, 256, 2), (32, 32, 64, 16, 512, 8), (3, 3, 64, 32, 64, 4)])
+def test_attention_decode_bulk_heads_per_block(k, nq, nkv, d, ps, split, heads):
+    """The bulk decode kernel with a given number of kv heads per block (fewer heads: more and shorter
+    blocks for small batches), many short splits merged by the block that finishes last, head counts
+    that the group does not divide; the counters are back at zero afterwards, and a second call on
+    the same counters gives the same bits.  A group that the sizes do not allow is refused."""
+    dtype = torch.bfloat16
+    lib = k.native.load("attention_tc", None)
+    if lib.erb_attention_decode_bulk_head_group(nkv, d, ps, split, heads) != heads:
+        pytest.skip("these sizes do not allow this group")
+    ctx_lens = [1, 63, 64, 65, 640, 513, 129, 1000]
+    case = paged_case(dtype, 290 + d + ps + heads, nq, nkv, d, ps, ctx_lens, [1] * len(ctx_lens))
+    scale = d ** -0.5
+    dev = {n: case[n].cuda() for n in ("q", "kp", "vp", "tables", "seq_of", "pos")}
+    n = len(ctx_lens)
+    max_splits = max((c - 1) // split + 1 for c in ctx_lens)
+    acc_n, ml_n = k.decode_scratch_floats(n, nq, d, max_splits)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tok = torch.arange(n, dtype=torch.int32).cuda()
+    outs = []
+    for _ in range(2):
+        part_acc = torch.full((acc_n,), float("nan"), device="cuda")
+        part_ml = torch.full((ml_n,), float("nan"), device="cuda")
+        out = torch.full((n, nq * d), float("nan"), dtype=dtype, device="cuda")
+        k.attention_decode_bulk(dev["q"], dev["kp"], dev["vp"], dev["tables"], tok, dev["pos"], out, nq, scale,
+                                part_acc, part_ml, max_splits, status, split_keys=split, head_group=heads)
+        torch.cuda.synchronize()
+        assert int(status) == 0
+        assert int(k.split_counters(out.device, 1).abs().sum()) == 0, "a counter was left standing"
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    want = attention_reference(case, nq, nkv, d, scale)
+    torch.testing.assert_close(outs[0].float().cpu(), want, **tol(dtype))
+    with pytest.raises(k.KernelError):
+        k.attention_decode_bulk(dev["q"], dev["kp"], dev["vp"], dev["tables"], tok, dev["pos"], out, nq, scale,
+                                part_acc, part_ml, max_splits, status, split_keys=split, head_group=3)
+
+
+def test_decode_plan_is_a_function_of_the_batch_and_a_bound_on_the_context(k):
+    """The plan (keys per split, heads per block) that a decode step takes: allowed by the kernel, at
+    most 64 splits for the bound, more blocks for a small batch than the default grouping gives, the
+    default for batches that fill the GPU anyway, nothing for the kernel that groups by itself."""
+    lib = k.native.load("attention_tc", None)
+    for n_seqs in (1, 2, 3, 8, 16, 64):
+        for bound in (128, 1024, 8192):
+            split, heads = k.choose_decode_plan(n_seqs, 32, bound, 16, 64)
+            assert split % 16 == 0 and -(-bound // split) <= 64
+            assert heads == 0 or lib.erb_attention_decode_bulk_head_group(32, 64, 16, split, heads) == heads
+    split, heads = k.choose_decode_plan(1, 32, 1024, 16, 64)
+    assert heads == 2 and 1 * 16 * -(-1024 // split) >= 128
+    assert k.choose_decode_plan(64, 32, 8192, 16, 64)[1] == 0
+    assert k.choose_decode_plan(8, 5, 8192, 16, 64, grouped=True) == (k.choose_decode_split(8, 5, 8192, 16, 64), 0)
+
+
 @pytest.mark.parametrize("nq,nkv,ps,split", [(15, 5, 16, 512), (9, 3, 16, 1024), (6, 2, 8, 128), (8, 1, 16, 256),
                                              (16, 8, 32, 512), (20, 10, 16, 2048), (24, 3, 64, 512), (4, 2, 128, 256)])
 def test_attention_decode_for_grouped_heads_on_tensor_cores(k, nq, nkv, ps, split):

@@ -149,7 +149,8 @@ def test_generation_with_graphs_and_lookahead_at_real_layer_sizes(which, tmp_pat
         prompts = [helpers.random_sequence(cfg["vocab"], n, 900 + n) for n in lens]
         options = dict(dtype="bfloat16", block_size=16, num_blocks=100, chunk_size=512, max_batch_size=3,
                        max_prefills_per_step=3, poison_freed_pages=True)
-        split = kernels.choose_decode_split(3, cfg["n_kv"], 1024, 16, cfg["head_dim"])
+        bound, granule = kernels.context_bound(-(-lens[0] // 16))
+        split = kernels.choose_decode_plan(3, cfg["n_kv"], bound * 16, 16, cfg["head_dim"], cfg["n_q"] != cfg["n_kv"], granule * 16)[0]
         assert lens[0] // split + 1 >= 3, f"splits of {split} keys: the longest request would have fewer than three"
         runs = {}
         for graphs, ahead in itertools.product((False, True), (False, True)):
@@ -226,8 +227,9 @@ def test_a_request_decodes_to_the_same_bits_whatever_shares_its_step(which, tmp_
     """Requests with the same prompt (each prefilled alone, so their caches hold the same bits in different
     pages) decode the same token: one alone, one beside 7 others, one beside 15.  The logits are equal bit
     for bit: up to 16 rows the products of a decode step add a row's terms in an order that does not depend
-    on the number of rows, the norms and the rotary epilogue work row by row, and with contexts below the
-    smallest split every sequence is one split of the attention kernel.  Beside 31 and 63 others the
+    on the number of rows, the norms and the rotary epilogue work row by row, and with ``batch_invariant``
+    the attention kernel cuts every sequence into the same splits and groups of heads whatever the batch
+    (the twins' context spans two splits).  Beside 31 and 63 others the
     layers' products are the library's (whose sums depend on the number of rows): there the logits agree
     within the band of two cuttings of a request."""
     import shutil
@@ -238,10 +240,10 @@ def test_a_request_decodes_to_the_same_bits_whatever_shares_its_step(which, tmp_
     folder = folder_for(tmp_path, which, "bfloat16")
     try:
         cfg = plain.read_config(folder)
-        engine = Engine.from_pretrained(folder, dtype="bfloat16", block_size=16, num_blocks=70 * 8, max_batch_size=70,
-                                        max_step_tokens=256, cuda_graphs=False)
+        engine = Engine.from_pretrained(folder, dtype="bfloat16", block_size=16, num_blocks=70 * 8 + 5 * 40, max_batch_size=70,
+                                        max_step_tokens=640, cuda_graphs=False, batch_invariant=True)
         runner = engine.runner
-        same = helpers.random_sequence(cfg["vocab"], 90, 5)
+        same = helpers.random_sequence(cfg["vocab"], 600, 5)
         twins = [f"x{i}" for i in range(5)]
         others = [f"o{i}" for i in range(63)]
         for i, rid in enumerate(twins + others):
