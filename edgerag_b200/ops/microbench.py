@@ -230,6 +230,60 @@ def step_kernels(a) -> dict:
             "prefill": table(p1, ("step", 1)), "decode": table(p2, ("step", a.iters))}
 
 
+def step_timeline(a) -> dict:
+    """Where a decode step's time goes when its kernels run as they do in serving: replayed from a CUDA
+    graph with chained launches, so that a kernel starts while the one before it drains.  The activity
+    tracer gives every kernel's start and end; a kernel's share of the critical path is the time from
+    the end of the kernels before it to its own end.  ``--layers`` layers of the SmolVLM-2.2B sizes,
+    ``--batch`` sequences at ``--context``; averages over the layers after the first, in microseconds
+    (they carry the tracer's overhead: read them as shares)."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..engine.engine import Engine, EngineOptions
+    from ..engine.step import StepEntry
+
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": a.layers, "hidden_size": 2048,
+           "num_attention_heads": a.heads, "num_key_value_heads": a.kv_heads, "head_dim": 64, "intermediate_size": 8192,
+           "vocab_size": 49155, "rope_theta": 273768.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+           "hidden_act": "silu", "max_position_embeddings": 8192, "pad_token_id": 0}
+    eng = Engine.from_config(cfg, 0, 0.02, EngineOptions(
+        dtype="bfloat16", block_size=16, num_blocks=a.batch * (a.context // 16 + 2) + 64, max_batch_size=a.batch + 2,
+        max_step_tokens=512 + a.batch, max_model_len=a.context + 8, cuda_graphs=True))
+    r = eng.runner
+    names = [f"d{i}" for i in range(a.batch)]
+    for n in names:
+        r.admit(n)
+        eng.cache.grow(n, a.context - 16)
+        eng.cache.advance(n, a.context - 16)
+    step = lambda: r.step([StepEntry(n, tokens=[5], want=[0]) for n in names])  # noqa: E731
+    for _ in range(4):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if "cuda" in str(e.device_type).lower() and "Memcpy" not in e.name),
+                    key=lambda e: e.time_range.start)
+    first = max(i for i, e in enumerate(events) if "embed_rows" in e.name)
+    events = events[first:]
+    names_of = [e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0][:48] for e in events]
+    norms = [i for i, n in enumerate(names_of) if n.startswith("add_rmsnorm")]
+    per_layer = norms[2] - norms[0] if len(norms) > 2 else len(events) - 1      # a layer: from its first norm to the next layer's
+    t0, frontier = events[0].time_range.start, events[0].time_range.end
+    shares: dict[tuple[int, str], list[float]] = {}
+    starts = []
+    for i, e in enumerate(events[1: 1 + per_layer * a.layers]):
+        if i % per_layer == 0:
+            starts.append(e.time_range.start)
+        name = names_of[1 + i]
+        shares.setdefault((i % per_layer, name), []).append(max(0.0, e.time_range.end - max(frontier, e.time_range.start)))
+        frontier = max(frontier, e.time_range.end)
+    rows = [{"kernel": name, "critical_us": round(sum(v[1:]) / max(1, len(v) - 1), 2)} for (_, name), v in sorted(shares.items())]
+    period = (starts[-1] - starts[0]) / max(1, len(starts) - 1) if len(starts) > 1 else 0.0
+    return {"case": "step-timeline", "layers": a.layers, "batch": a.batch, "context": a.context, "replayed_from_graph": r.graph_replays > 0,
+            "layer_period_us": round(period, 2), "step_us": round(events[-1].time_range.end - t0, 1), "kernels_of_a_layer": rows}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="edgerag_b200.ops.microbench", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -270,12 +324,18 @@ def main(argv=None) -> int:
     k.add_argument("--tokens", type=int, default=2048)
     k.add_argument("--heads", type=int, default=32)
     k.add_argument("--kv-heads", type=int, default=32)
+    t = sub.add_parser("step-timeline", parents=[common])
+    t.add_argument("--layers", type=int, default=4)
+    t.add_argument("--batch", type=int, default=8)
+    t.add_argument("--context", type=int, default=640)
+    t.add_argument("--heads", type=int, default=32)
+    t.add_argument("--kv-heads", type=int, default=32)
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
     fn = {"decode-attention": decode_attention, "prefill-attention": prefill_attention, "linear": linear,
-          "step-kernels": step_kernels}[a.case]
+          "step-kernels": step_kernels, "step-timeline": step_timeline}[a.case]
     load_peaks(a.peaks)
     result = fn(a)
     result["peaks"] = PEAKS_FROM
