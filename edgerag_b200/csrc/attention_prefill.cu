@@ -24,6 +24,11 @@
 // that it has become far too low (P is a floating-point number: a reference that is low by twenty powers
 // of two costs no precision).  So most tiles need no search for a maximum and no rescaling of O.
 //
+// A portion that is short against its past (512 new tokens after 7,000 cached ones) gives few blocks,
+// each with a long walk over the keys.  The launch may then cut every block's key tiles into
+// `key_splits` ranges, one block per range (blockIdx.z): a block leaves its rows' unnormalised O, reference
+// maximum and sum in scratch, and a second kernel merges the ranges of each row.
+//
 // Every wait is bounded: a thread that gives up raises a block-wide flag, every other wait of the
 // block then ends too, the block records a code in *status, lets its copies land, frees its TMEM
 // and returns.
@@ -71,7 +76,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
                          const __nv_bfloat16* __restrict__ q, int q_row_stride,
                          const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
                          const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, int out_row_stride,
-                         int n_seqs, int nq, int nkv, int page_size, float scale_log2, int* __restrict__ status) {
+                         int n_seqs, int nq, int nkv, int page_size, float scale_log2, int* __restrict__ status,
+                         int key_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;             // the swizzle repeats every 1024 bytes
@@ -129,6 +135,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   // The last key tile holds `valid_last` keys; the second product stops at the 16 keys that hold the last one.
   const int valid_last = last_key - (n_kv - 1) * BN + 1;
   const int ksteps_last = (valid_last + 15) >> 4;
+  // This block's range of key tiles [j0, j1) (all of them without splits), and where each query tile stops in it.
+  const int per_split = (n_kv + key_splits - 1) / key_splits;
+  const int j0 = (int)blockIdx.z * per_split, j1 = min(n_kv, j0 + per_split);
+  const int n_end[2] = {min(n_t[0], j1), min(n_t[1], j1)};
 
   if (warp < kSoftmaxWarps) {
     // Q tiles: each softmax thread copies its share (a warp covers whole 128-byte rows); rows past the
@@ -173,82 +183,84 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       __syncwarp();
       if (page >= 0) tma_load_rows(dst + (uint32_t)lane * page_bytes, map, (page * nkv + kvh) * page_size, full);
     };
-    int page_next = page_of(0);
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const int ks = j & (kKStages - 1), vs = j & (kVStages - 1);
+    int page_next = page_of(j0);
+    for (int j = j0; j < j1 && ok; ++j) {
+      const int jj = j - j0;                            // stages and barrier phases count from the block's first tile
+      const int ks = jj & (kKStages - 1), vs = jj & (kVStages - 1);
       const int page = page_next;
       page_next = page_of(j + 1);
-      if (j >= kKStages) ok = wait(kBarKEmpty + ks, ((j / kKStages) - 1) & 1);
+      if (jj >= kKStages) ok = wait(kBarKEmpty + ks, ((jj / kKStages) - 1) & 1);
       if (!ok) break;
       bring(j, page, &map_k, sK + ks * kKvBytes, bar(kBarKFull + ks));
-      copies_k = j + 1;
-      if (j >= kVStages) ok = wait(kBarVEmpty + vs, ((j / kVStages) - 1) & 1);
+      copies_k = jj + 1;
+      if (jj >= kVStages) ok = wait(kBarVEmpty + vs, ((jj / kVStages) - 1) & 1);
       if (!ok) break;
       bring(j, page, &map_v, sV + vs * kKvBytes, bar(kBarVFull + vs));
-      copies_v = j + 1;
+      copies_v = jj + 1;
     }
   } else if (warp == kIssueWarp) {
     // ---- one thread issues the products (a lone thread runs an instruction every few clocks: its code is kept short) ----
-    if (lane == 0) {
+    if (lane == 0 && j0 < j1) {
       const uint64_t dq[2] = {make_desc(sQ), make_desc(sQ + kQBytes)};
       const uint64_t dk0 = make_desc(sK), dv0 = make_desc(sV);
       const uint32_t d_s[2] = {tmem + kColS, tmem + kColS + BN}, d_o[2] = {tmem + kColO, tmem + kColO + HD},
                      a_p[2] = {tmem + kColP, tmem + kColP + BN / 2};
       bool ok = true;
       auto issue_s = [&](int t, int j) {                // S_t(j) = Q_t K(j)^T
-        const uint64_t dk = dk0 + (uint64_t)((j & (kKStages - 1)) * (kKvBytes >> 4));
+        const uint64_t dk = dk0 + (uint64_t)(((j - j0) & (kKStages - 1)) * (kKvBytes >> 4));
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) mma_bf16(d_s[t], dq[t] + 2 * k, dk + 2 * k, kIdescS, k > 0);
         mma_commit(bar(kBarSFull + t));
       };
       auto issue_pv = [&](int t, int j) {               // O_t += P_t(j) V(j): 16 keys per step, 8 columns of P, 2048 bytes of V
-        const uint64_t dv = dv0 + (uint64_t)((j & (kVStages - 1)) * (kKvBytes >> 4));
+        const uint64_t dv = dv0 + (uint64_t)(((j - j0) & (kVStages - 1)) * (kKvBytes >> 4));
         if (j < n_kv - 1) {
 #pragma unroll
           for (int k = 0; k < BN / 16; ++k)
-            mma_bf16_a_tmem(d_o[t], a_p[t] + k * 8, dv + (uint64_t)(k * (2048 >> 4)), kIdescO, (j > 0 || k > 0) ? 1u : 0u);
+            mma_bf16_a_tmem(d_o[t], a_p[t] + k * 8, dv + (uint64_t)(k * (2048 >> 4)), kIdescO, (j > j0 || k > 0) ? 1u : 0u);
         } else {
           for (int k = 0; k < ksteps_last; ++k)
-            mma_bf16_a_tmem(d_o[t], a_p[t] + k * 8, dv + (uint64_t)(k * (2048 >> 4)), kIdescO, (j > 0 || k > 0) ? 1u : 0u);
+            mma_bf16_a_tmem(d_o[t], a_p[t] + k * 8, dv + (uint64_t)(k * (2048 >> 4)), kIdescO, (j > j0 || k > 0) ? 1u : 0u);
         }
         mma_commit(bar(kBarPvDone + t));
       };
       ok = mbar_wait_or_abort(bar(kBarKFull + 0), 0, s_abort);
       if (ok) {
-        if (n_t[0] > 0) issue_s(0, 0);
-        if (n_t[1] > 0) issue_s(1, 0);
+        if (j0 < n_end[0]) issue_s(0, j0);
+        if (j0 < n_end[1]) issue_s(1, j0);
         mma_commit(bar(kBarKEmpty + 0));
       }
-      for (int j = 0; j < n_kv && ok; ++j) {
+      for (int j = j0; j < j1 && ok; ++j) {
+        const int jj = j - j0;
         for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= n_t[t]) continue;
-          ok = mbar_wait_or_abort(bar(kBarPFull + t), j & 1, s_abort);   // P_t(j) is written and S_t(j) has been read
+          if (j >= n_end[t]) continue;
+          ok = mbar_wait_or_abort(bar(kBarPFull + t), jj & 1, s_abort);   // P_t(j) is written and S_t(j) has been read
           if (!ok) break;
           fence_after_sync();
-          if (j + 1 < n_t[t]) {
-            const bool first_user = (t == 0) || (j + 1 >= n_t[0]);
-            const bool last_user = (t == 1) || (j + 1 >= n_t[1]);
-            if (first_user) ok = mbar_wait_or_abort(bar(kBarKFull + ((j + 1) & (kKStages - 1))), ((j + 1) / kKStages) & 1, s_abort);
+          if (j + 1 < n_end[t]) {
+            const bool first_user = (t == 0) || (j + 1 >= n_end[0]);
+            const bool last_user = (t == 1) || (j + 1 >= n_end[1]);
+            if (first_user) ok = mbar_wait_or_abort(bar(kBarKFull + ((jj + 1) & (kKStages - 1))), ((jj + 1) / kKStages) & 1, s_abort);
             if (!ok) break;
             issue_s(t, j + 1);
-            if (last_user) mma_commit(bar(kBarKEmpty + ((j + 1) & (kKStages - 1))));
+            if (last_user) mma_commit(bar(kBarKEmpty + ((jj + 1) & (kKStages - 1))));
           }
-          const bool first_user = (t == 0) || (j >= n_t[0]);
-          const bool last_user = (t == 1) || (j >= n_t[1]);
+          const bool first_user = (t == 0) || (j >= n_end[0]);
+          const bool last_user = (t == 1) || (j >= n_end[1]);
           if (first_user) {
-            ok = mbar_wait_or_abort(bar(kBarVFull + (j & (kVStages - 1))), (j / kVStages) & 1, s_abort);
+            ok = mbar_wait_or_abort(bar(kBarVFull + (jj & (kVStages - 1))), (jj / kVStages) & 1, s_abort);
             if (!ok) break;
             if (j == n_kv - 1) {
               // Rows behind the last key may hold anything (unwritten slots of the page, an earlier tile):
               // their P is zero, but 0 * NaN would spoil the product, so they are made zero.
-              uint8_t* v_tile = smem + (sV - base) + (j & (kVStages - 1)) * kKvBytes;
+              uint8_t* v_tile = smem + (sV - base) + (jj & (kVStages - 1)) * kKvBytes;
               for (int idx = 0; idx < (ksteps_last * 16 - valid_last) * 8; ++idx)
                 *reinterpret_cast<uint4*>(v_tile + swz(valid_last + (idx >> 3), idx & 7)) = make_uint4(0, 0, 0, 0);
               fence_async_proxy();
             }
           }
           issue_pv(t, j);
-          if (last_user) mma_commit(bar(kBarVEmpty + (j & (kVStages - 1))));
+          if (last_user) mma_commit(bar(kBarVEmpty + (jj & (kVStages - 1))));
         }
       }
     }
@@ -271,8 +283,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       ok = __all_sync(0xffffffffu, ok) != 0;             // the same answer for every lane: TMEM loads are collective
     };
     float m_ref = -INFINITY, l_run = 0.f;                // l_run: this thread's half of the row's sum
-    for (int j = 0; j < n_t[t]; ++j) {
-      wait(kBarSFull + t, j & 1);
+    for (int j = j0; j < n_end[t]; ++j) {
+      wait(kBarSFull + t, (j - j0) & 1);
       if (!ok) break;
       fence_after_sync();
       const int key0 = j * BN + half * 64;
@@ -284,7 +296,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       // O and the running sum rescaled, and the tile's P computed again.
       float l_tile = 0.f;
       uint32_t packed[32];
-      bool search = j == 0;
+      bool search = j == j0;
       for (;;) {
         if (search) {
           float m_half = -INFINITY;
@@ -298,16 +310,18 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           }
           *mine = m_half;
           named_barrier(pair_barrier, 64);
-          const float m_tile = fmaxf(m_half, *partners) * scale_log2;   // scale > 0: the maximum of the scaled scores
+          // (scale > 0: the maximum of the scaled scores.  A range of keys may begin with a tile of which a row
+          // sees nothing: its reference then stays at a finite floor, so that exp2(-inf - reference) is 0, not NaN.)
+          const float m_tile = fmaxf(fmaxf(m_half, *partners) * scale_log2, -1e30f);
           float alpha = 1.f;
           if (m_tile > m_ref) {
             alpha = fast_exp2(m_ref - m_tile);                          // 0 on the first tile
             m_ref = m_tile;
           }
           l_run *= alpha;
-          if (j > 0) {
+          if (j > j0) {
             // O is rescaled in TMEM: P V of tile j-1 must have landed first
-            wait(kBarPvDone + t, (j - 1) & 1);
+            wait(kBarPvDone + t, (j - 1 - j0) & 1);
             if (!ok) break;
             fence_after_sync();
             float acc[32];
@@ -349,9 +363,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         search = true;
       }
       if (!ok) break;
-      if (j > 0) {
+      if (j > j0) {
         // P V of tile j-1 has to be done before its P is overwritten
-        wait(kBarPvDone + t, (j - 1) & 1);
+        wait(kBarPvDone + t, (j - 1 - j0) & 1);
         if (!ok) break;
         fence_after_sync();
       }
@@ -362,12 +376,27 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarPFull + t));
     }
-    if (n_t[t] > 0) {
-      wait(kBarPvDone + t, (n_t[t] - 1) & 1);
+    // where this row's share of a split goes: [token][head][split] records of HD floats, and of (maximum, sum)
+    const size_t record = ((size_t)(q0 + t * BM + row) * nq + h) * key_splits + blockIdx.z;
+    if (n_end[t] <= j0) {
+      // nothing of this range is visible to this query tile: an empty record for the merge
+      if (key_splits > 1 && half == 0 && row < rows_t[t]) { part_ml[record * 2] = -INFINITY; part_ml[record * 2 + 1] = 0.f; }
+    } else {
+      wait(kBarPvDone + t, (n_end[t] - 1 - j0) & 1);
       fence_after_sync();
       mine[2 * 2 * BM] = l_run;                          // (a slot of its own: the partner may still be reading a maximum)
       named_barrier(pair_barrier, 64);
-      if (ok) {
+      if (ok && key_splits > 1) {
+        float acc[32];
+        tmem_ld32(t_o, acc);
+        tmem_ld_wait();
+        if (row < rows_t[t]) {
+          float4* dst = reinterpret_cast<float4*>(part_o + record * HD + half * 32);
+#pragma unroll
+          for (int d = 0; d < 8; ++d) dst[d] = make_float4(acc[4 * d], acc[4 * d + 1], acc[4 * d + 2], acc[4 * d + 3]);
+          if (half == 0) { part_ml[record * 2] = m_ref; part_ml[record * 2 + 1] = l_run + partners[2 * 2 * BM]; }
+        }
+      } else if (ok) {
         const float inv = 1.f / (l_run + partners[2 * 2 * BM]);
         __nv_bfloat16* dst = out + (size_t)(q0 + t * BM + row) * out_row_stride + (size_t)h * HD + half * 32;
         float acc[32];
@@ -407,6 +436,32 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   }
 }
 
+// Merges the key ranges of each (token, head): the ranges' reference maxima are in the log2 domain; a
+// range that saw no key has sum 0.  One warp per (token, head), a lane for two neighbouring elements.
+__global__ void __launch_bounds__(128)
+attention_prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+                               int out_row_stride, int first_row, int n_rows, int nq, int key_splits) {
+  chain_wait();
+  const int pair = (int)(blockIdx.x * 4 + (threadIdx.x >> 5)), lane = threadIdx.x & 31;
+  if (pair >= n_rows * nq) return;
+  const int row = first_row + pair / nq, h = pair % nq;
+  const size_t record = ((size_t)row * nq + h) * key_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < key_splits; ++s) m = fmaxf(m, part_ml[(record + s) * 2]);
+  float l = 0.f, o0 = 0.f, o1 = 0.f;
+  for (int s = 0; s < key_splits; ++s) {
+    const float ls = part_ml[(record + s) * 2 + 1];
+    if (ls == 0.f) continue;                              // (its O was never written)
+    const float w = exp2f(part_ml[(record + s) * 2] - m);
+    const float2 o = *reinterpret_cast<const float2*>(part_o + (record + s) * HD + 2 * lane);
+    l += ls * w;
+    o0 += o.x * w;
+    o1 += o.y * w;
+  }
+  const float inv = 1.f / l;
+  *reinterpret_cast<__nv_bfloat162*>(out + (size_t)row * out_row_stride + (size_t)h * HD + 2 * lane) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+}
+
 }  // namespace
 
 // Rows of one (sequence, head) that a block takes: the caller sizes the grid with it.
@@ -422,12 +477,19 @@ ERB_EXPORT int erb_attention_prefill_tc_supported(int head_dim, int page_size) {
 // sequences to process (consecutive rows of block_tables); n_blocks: sum over them of
 // ceil(length / 256) (an upper bound is fine); n_pool_pages: pages of k_pages / v_pages (the tensor
 // maps cover the whole pool).  status: device int, set non-zero if a block gave up waiting.
+// key_splits > 1: every block's key tiles are cut into that many ranges (for portions that are short
+// against their past); first_row and n_rows name the rows of q / out that the sequences cover (they
+// are consecutive), part_o has room for (first_row + n_rows) * nq * key_splits * 64 floats and part_ml
+// for (first_row + n_rows) * nq * key_splits * 2.
 ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                         int n_pool_pages, const int* block_tables, int max_pages,
                                         const int* seq_starts, const int* positions, void* out, int out_row_stride,
                                         int n_seqs, int n_blocks, int nq, int nkv, int head_dim, int page_size,
-                                        float scale, int* status, void* stream) {
+                                        float scale, int* status, int key_splits, int first_row, int n_rows,
+                                        float* part_o, float* part_ml, void* stream) {
   if (n_seqs <= 0 || n_blocks <= 0) return ERB_OK;
+  if (key_splits < 1 || key_splits > 64 || (key_splits > 1 && (!part_o || !part_ml || first_row < 0 || n_rows <= 0 || ((uintptr_t)part_o & 15))))
+    return fail(ERB_ERR_ARG, "attention_prefill_tc: bad split arguments");
   if (!erb_attention_prefill_tc_supported(head_dim, page_size))
     return fail(ERB_ERR_UNSUPPORTED, "attention_prefill_tc: head_dim %d with pages of %d (takes 64 with 8, 16, 32, 64 or 128)",
                 head_dim, page_size);
@@ -452,8 +514,11 @@ ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const v
     configured = true;
   }
   const float scale_log2 = scale * 1.4426950408889634f;
-  launch_chained(attention_prefill_kernel, dim3(nq, n_blocks), dim3(kThreads), kSmemBytes, (cudaStream_t)stream, mk, mv,
+  launch_chained(attention_prefill_kernel, dim3(nq, n_blocks, key_splits), dim3(kThreads), kSmemBytes, (cudaStream_t)stream, mk, mv,
                  (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, seq_starts, positions,
-                 (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv, page_size, scale_log2, status);
-  return check_launch("attention_prefill_tc");
+                 (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv, page_size, scale_log2, status, key_splits, part_o, part_ml);
+  if ((rc = check_launch("attention_prefill_tc")) || key_splits == 1) return rc;
+  launch_chained(attention_prefill_merge_kernel, dim3((n_rows * nq + 3) / 4), dim3(128), 0, (cudaStream_t)stream, part_o, part_ml,
+                 (__nv_bfloat16*)out, out_row_stride, first_row, n_rows, nq, key_splits);
+  return check_launch("attention_prefill_merge");
 }

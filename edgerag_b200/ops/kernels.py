@@ -50,7 +50,7 @@ _SIGNATURES = {
                              c_int, c_int, c_float, c_void_p],
     "erb_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                 c_void_p],
+                                 c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "erb_attention_decode_bulk": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
@@ -64,7 +64,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_attention_decode": 2, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
+_LAUNCHES = {"erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
 TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
 
@@ -691,15 +691,37 @@ def prefill_tc_blocks(q_lens) -> int:
     return sum(-(-int(n) // PREFILL_TC_ROWS) for n in q_lens)
 
 
+def prefill_tc_key_splits(n_blocks: int, n_q_heads: int, max_keys: int, device: torch.device) -> int:
+    """Ranges to cut every block's keys into: 1 unless the portions give far fewer blocks than the GPU has
+    SMs and the walk over the keys is long (512 new tokens after 7,000 cached ones: 30 to 64 blocks of
+    59 key tiles each take 131 us whatever their number; cut so that the blocks fill one wave, 4 tiles
+    a range at least).  ``max_keys``: a bound on the longest context that steps of one layout share."""
+    sms = _sms(device)
+    blocks = n_blocks * n_q_heads
+    tiles = -(-max_keys // 128)
+    if blocks * 2 > sms or tiles < 8:
+        return 1
+    return max(1, min(sms // blocks, tiles // 4, 16))
+
+
+def prefill_tc_scratch_floats(n_rows: int, n_q_heads: int, key_splits: int) -> tuple[int, int]:
+    """Floats of ``part_o`` and ``part_ml`` for ``attention_prefill_tc`` with key splits over the first ``n_rows`` rows of the batch."""
+    return n_rows * n_q_heads * key_splits * 64, n_rows * n_q_heads * key_splits * 2
+
+
 def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                          seq_starts: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_blocks: int,
-                         n_q_heads: int, scale: float, status: torch.Tensor) -> None:
+                         n_q_heads: int, scale: float, status: torch.Tensor, key_splits: int = 1, first_row: int = 0,
+                         part_o: torch.Tensor | None = None, part_ml: torch.Tensor | None = None) -> None:
     """Causal attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64, no window).
 
     ``qkv`` / ``out``: row t is token t of the batch (the q heads lead each qkv row);
     ``seq_starts`` int32 ``[n + 1]``: token offsets of the n sequences to process, whose block tables
     are the n rows of ``block_tables``; ``n_blocks``: ``prefill_tc_blocks`` of their lengths (an upper
-    bound is fine).
+    bound is fine).  ``key_splits`` > 1 (``prefill_tc_key_splits``): every block's keys are cut into
+    that many ranges, each a block of its own, and a second kernel merges them; the sequences'
+    tokens are then rows ``first_row`` to the end of ``qkv``, and ``part_o`` / ``part_ml`` are float
+    scratch of ``prefill_tc_scratch_floats(qkv rows, heads, key_splits)``.
     """
     _need(qkv, "qkv", torch.bfloat16, contiguous=False); _need(k_pages, "k_pages", torch.bfloat16)
     _need(v_pages, "v_pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
@@ -709,10 +731,18 @@ def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     n_seqs = seq_starts.numel() - 1
     if qkv.stride(1) != 1 or out.stride(1) != 1 or block_tables.shape[0] < n_seqs or v_pages.shape != k_pages.shape:
         raise KernelError("attention_prefill_tc: layout disagrees")
+    if key_splits > 1:
+        _need(part_o, "part_o", torch.float32); _need(part_ml, "part_ml", torch.float32)
+        need_o, need_ml = prefill_tc_scratch_floats(qkv.shape[0], n_q_heads, key_splits)
+        if part_o is None or part_ml is None or part_o.numel() < need_o or part_ml.numel() < need_ml or not 0 <= first_row < qkv.shape[0]:
+            raise KernelError("attention_prefill_tc: scratch for the key ranges is missing or too small")
     _call(_fn("attention_prefill", None, "erb_attention_prefill_tc"), qkv.data_ptr(), qkv.stride(0), k_pages.data_ptr(),
           v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], seq_starts.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), n_seqs, int(n_blocks), n_q_heads, nkv, d, page_size,
-          float(scale), status.data_ptr(), _stream())
+          float(scale), status.data_ptr(), int(key_splits), int(first_row), qkv.shape[0] - int(first_row), _ptr(part_o), _ptr(part_ml),
+          _stream())
+    if key_splits > 1:
+        launch_counts["own"] += 1          # the merge of the ranges
 
 
 # --- sampling --------------------------------------------------------------------------------

@@ -137,8 +137,12 @@ def prefill_attention(a) -> dict:
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     scale = a.head_dim ** -0.5
     if a.kernel == "tc":
-        fn = lambda: kernels.attention_prefill_tc(qkv, kp, vp, tables, starts, pos, out, kernels.prefill_tc_blocks([a.tokens]), a.heads,  # noqa: E731
-                                                  scale, status)
+        blocks = kernels.prefill_tc_blocks([a.tokens])
+        ranges = a.key_splits or kernels.prefill_tc_key_splits(blocks, a.heads, total, qkv.device)
+        need_o, need_ml = kernels.prefill_tc_scratch_floats(a.tokens, a.heads, ranges)
+        part_o, part_ml = torch.empty(need_o, device="cuda"), torch.empty(need_ml, device="cuda")
+        fn = lambda: kernels.attention_prefill_tc(qkv, kp, vp, tables, starts, pos, out, blocks, a.heads, scale, status,  # noqa: E731
+                                                  key_splits=ranges, part_o=part_o, part_ml=part_ml)
     else:
         fn = lambda: kernels.attention_rows(qkv, kp, vp, tables, seq_of, pos, out, a.heads, scale)  # noqa: E731
     us = _time(fn, a.iters, a.warmup)
@@ -308,6 +312,7 @@ def main(argv=None) -> int:
     p = sub.add_parser("prefill-attention", parents=[common, att])
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--past", type=int, default=0)
+    p.add_argument("--key-splits", type=int, default=0, help="ranges every block's keys are cut into; 0: the engine's choice")
     p.add_argument("--kernel", choices=["tc", "general"], default="tc")
     g = sub.add_parser("linear", parents=[common])
     g.add_argument("--m", type=int, default=8)

@@ -100,8 +100,17 @@ class Attention(Mixer):
                                          out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits,
                                          window=self.window, split_keys=split)
         if n > nd and kernels.prefill_tc_supported(self.dtype, d, self.window, ctx.page_size):
-            kernels.attention_prefill_tc(qkv, k_pages, v_pages, tables[nd:], ctx.seq_starts[nd:], ctx.positions, out,
-                                         kernels.prefill_tc_blocks(ctx.host_q_len[nd:]), self.n_q, self.scale, ctx.status)
+            blocks = kernels.prefill_tc_blocks(ctx.host_q_len[nd:])
+            # a portion that is short against its past: its few blocks' keys are cut into ranges
+            ranges = kernels.prefill_tc_key_splits(blocks, self.n_q, ctx.max_keys_bound(), qkv.device)
+            part_o = part_ml = None
+            if ranges > 1:
+                need_o, need_ml = kernels.prefill_tc_scratch_floats(n, self.n_q, ranges)
+                part_o = ctx.buf("attn.range_o", (need_o,), torch.float32)
+                part_ml = ctx.buf("attn.range_ml", (need_ml,), torch.float32)
+            kernels.attention_prefill_tc(qkv, k_pages, v_pages, tables[nd:], ctx.seq_starts[nd:], ctx.positions, out, blocks,
+                                         self.n_q, self.scale, ctx.status, key_splits=ranges, first_row=nd, part_o=part_o,
+                                         part_ml=part_ml)
         elif n > nd:
             kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:],
                                    out[nd:], self.n_q, self.scale, window=self.window)

@@ -606,10 +606,20 @@ def test_attention_finds_one_far_key(k, dtype):
     torch.testing.assert_close(out_d.float().cpu(), want[:1], **tol(dtype))
 
 
-@pytest.mark.parametrize("nq,nkv,ps", [(4, 2, 16), (2, 2, 8), (3, 1, 64)])
-def test_attention_prefill_tensor_cores(k, nq, nkv, ps):
+def prefill_ranges(k, n_rows, nq, ranges):
+    """Keyword arguments of ``attention_prefill_tc`` for ``ranges`` key ranges (scratch poisoned with NaN)."""
+    if ranges == 1:
+        return {}
+    need_o, need_ml = k.prefill_tc_scratch_floats(n_rows, nq, ranges)
+    return dict(key_splits=ranges, part_o=torch.full((need_o,), float("nan"), device="cuda"),
+                part_ml=torch.full((need_ml,), float("nan"), device="cuda"))
+
+
+@pytest.mark.parametrize("nq,nkv,ps,ranges", [(4, 2, 16, 1), (2, 2, 8, 1), (3, 1, 64, 1), (4, 2, 16, 3), (3, 1, 64, 2), (2, 2, 8, 7)])
+def test_attention_prefill_tensor_cores(k, nq, nkv, ps, ranges):
     """The tcgen05 kernel for prompt portions: whole prompts, a portion that continues from the cache
-    across a tile edge, lengths around 128 and 256, shuffled pages with NaN in every unwritten slot."""
+    across a tile edge, lengths around 128 and 256, shuffled pages with NaN in every unwritten slot;
+    with every block's keys cut into ranges (more ranges than some blocks have key tiles: empty ranges)."""
     d = 64
     ctx_lens = [37, 500, 128, 129, 256, 700]
     q_lens = [37, 300, 128, 129, 2, 257]
@@ -624,7 +634,8 @@ def test_attention_prefill_tensor_cores(k, nq, nkv, ps):
     out = torch.full((n_tok, nq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     n_tiles = k.prefill_tc_blocks(q_lens)
-    k.attention_prefill_tc(qkv, dev["kp"], dev["vp"], dev["tables"], starts, dev["pos"], out, n_tiles, nq, scale, status)
+    k.attention_prefill_tc(qkv, dev["kp"], dev["vp"], dev["tables"], starts, dev["pos"], out, n_tiles, nq, scale, status,
+                           **prefill_ranges(k, n_tok, nq, ranges))
     torch.cuda.synchronize()
     assert int(status) == 0, f"the kernel gave up waiting on the tensor cores (status {int(status)})"
     want = attention_reference(case, nq, nkv, d, scale)
@@ -650,8 +661,8 @@ def plant_strong_keys(case, seq, nkv, d, ps, places, dtype, axis=5):
             case["kp"][page, h, off] = key.to(dtype)
 
 
-@pytest.mark.parametrize("nq,nkv,ps", [(4, 2, 16), (2, 2, 8)])
-def test_attention_prefill_tensor_cores_when_row_maxima_jump(k, nq, nkv, ps):
+@pytest.mark.parametrize("nq,nkv,ps,ranges", [(4, 2, 16, 1), (2, 2, 8, 1), (4, 2, 16, 2), (2, 2, 8, 5)])
+def test_attention_prefill_tensor_cores_when_row_maxima_jump(k, nq, nkv, ps, ranges):
     """Random scores never move a row's maximum much after the first tile, so the path that rescales the
     output accumulator when a maximum jumps would go untested.  Here keys with scores of 10, 25 and 40
     (natural-log units: each more than 2^8 above everything before it) sit in later tiles of the keys, for
@@ -675,7 +686,7 @@ def test_attention_prefill_tensor_cores_when_row_maxima_jump(k, nq, nkv, ps):
     out = torch.full((n_tok, nq * d), float("nan"), dtype=dtype, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     k.attention_prefill_tc(qkv, dev["kp"], dev["vp"], dev["tables"], starts, dev["pos"], out,
-                           k.prefill_tc_blocks(q_lens), nq, scale, status)
+                           k.prefill_tc_blocks(q_lens), nq, scale, status, **prefill_ranges(k, n_tok, nq, ranges))
     torch.cuda.synchronize()
     assert int(status) == 0
     want = attention_reference(case, nq, nkv, d, scale)
