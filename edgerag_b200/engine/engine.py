@@ -88,6 +88,9 @@ class EngineOptions:
     #: bits whatever shares its step; off, the attention kernel's shape follows the batch, which is
     #: faster for small batches and short contexts
     batch_invariant: bool = False
+    #: captured steps fill their single-token rows up to the next of a few sizes (1, 2, 4, 8, 16, 24, ...), so
+    #: that a change in the number of running requests seldom needs another graph
+    pad_decodes: bool = True
 
 
 @dataclass
@@ -140,7 +143,8 @@ class Engine:
         self.pools = DevicePools(layout, options.block_size, n_pages, options.max_batch_size, self.dtype,
                                  self.device, poison=options.poison_freed_pages)
         self.runner = ModelRunner(model, self.cache, self.pools, max_step_tokens=max_step,
-                                  cuda_graphs=options.cuda_graphs, batch_invariant=options.batch_invariant)
+                                  cuda_graphs=options.cuda_graphs, batch_invariant=options.batch_invariant,
+                                  pad_decodes=options.pad_decodes)
         self.scheduler = Scheduler(self.cache, SchedulerConfig(
             max_batch_size=options.max_batch_size, prefill_chunk_size=options.chunk_size,
             max_prefills_per_step=options.max_prefills_per_step, max_step_tokens=max_step,

@@ -96,6 +96,7 @@ class StepContext:
         self.batch_invariant = runner.batch_invariant
         self.status = runner.status
         self.n_tokens = self.n_seqs = self.n_decode = self.n_wanted = self.n_fed_back = 0
+        self.n_wanted_real = 0                       # wanted rows that belong to entries (the others to filler rows)
         self.token_ids = self.embed_row = self.positions = self.seq_of_token = None
         self.token_of_seq = self.want_rows = self.state_slots = self.seq_starts = None
         self.embeds: torch.Tensor | None = None
@@ -143,13 +144,25 @@ class StepContext:
         return most
 
 
+def _fill_to(n: int) -> int:
+    """The size that ``n`` single-token rows of a captured step are filled up to: the next power of two up to 8, then the next multiple of 8."""
+    return 1 << (n - 1).bit_length() if n <= 8 else -(-n // 8) * 8
+
+
 class ModelRunner:
     """Owns the model, the cache and the scratch of one device, and runs steps on them."""
 
     def __init__(self, model, cache: CacheManager, pools: DevicePools, max_step_tokens: int,
-                 check_status: bool = False, cuda_graphs: bool = False, batch_invariant: bool = False) -> None:
+                 check_status: bool = False, cuda_graphs: bool = False, batch_invariant: bool = False,
+                 pad_decodes: bool = True) -> None:
         self.model = model
         self.batch_invariant = bool(batch_invariant)
+        #: steps whose tokens are all ids get their single-token sequences (and their wanted rows) filled up
+        #: to the next of a few sizes with rows that read one cached key, write nothing and are dropped
+        #: again, so that the number of running requests, which changes all the time in serving, changes
+        #: the layout (and with it the captured graph) only now and then; done whether or not graphs are
+        #: on, so that turning them on changes no bit
+        self.pad_decodes = bool(pad_decodes)
         self.cache = cache
         self.pools = pools
         self.device = pools.device
@@ -248,8 +261,21 @@ class ModelRunner:
         # Single-token entries first; a stable order otherwise.
         order = sorted(range(len(entries)), key=lambda i: (entries[i].n_tokens != 1, i))
         ordered = [entries[i] for i in order]
-        n_seqs = len(ordered)
         n_decode = sum(1 for e in ordered if e.n_tokens == 1)
+        # A step whose layout is fully described by a small key can be replayed from a CUDA graph:
+        # single tokens, and portions of prompts given as ids (their lengths are part of the key).
+        graphable = self.graphs_enabled and all(e.embeds is None for e in ordered)
+        # Filler rows between the single tokens and the portions (None in `rows`): see `pad_decodes`.
+        n_fill = 0
+        if self.pad_decodes and n_decode and all(e.embeds is None for e in ordered) and not self.cache.layout.states:
+            n_fill = _fill_to(n_decode) - n_decode
+            if total + n_fill > self.max_step_tokens:
+                n_fill = 0
+        rows: list[StepEntry | None] = ordered[:n_decode] + [None] * n_fill + ordered[n_decode:]
+        origins = order[:n_decode] + [-1] * n_fill + order[n_decode:]
+        total += n_fill
+        n_decode += n_fill
+        n_seqs = len(rows)
         ps = self.cache.page_size
 
         token_ids = np.zeros(total, np.int32)
@@ -264,9 +290,6 @@ class ModelRunner:
         for e in ordered:
             rc = self.cache.requests[e.request_id]
             max_pages = max(max_pages, max((len(t.pages) for t in rc.tables), default=1))
-        # A step whose layout is fully described by a small key can be replayed from a CUDA graph:
-        # single tokens, and portions of prompts given as ids (their lengths are part of the key).
-        graphable = self.graphs_enabled and all(e.embeds is None for e in ordered)
         bound_pages, granule_pages = kernels.context_bound(max_pages)
         if graphable:
             # a captured step has a fixed layout: block tables padded to a power of two of pages
@@ -277,7 +300,18 @@ class ModelRunner:
         n_embed_rows = 0
         ctx = StepContext(self)
         t0 = 0
-        for s, (orig, e) in enumerate(zip(order, ordered)):
+        for s, (orig, e) in enumerate(zip(origins, rows)):
+            if e is None:
+                # a filler: token 0 at position 0 of a sequence whose table names page 0 only; it reads that
+                # page's first key (whatever it holds: the row's results go nowhere) and has no cache slot
+                seq_of_token[t0] = s
+                token_of_seq[s] = t0
+                seq_starts[s + 1] = t0 + 1
+                ctx.host_q_len.append(1)
+                ctx.host_positions_last.append(0)
+                ctx.host_state_slots.append(0)
+                t0 += 1
+                continue
             rc = self.cache.requests[e.request_id]
             n = e.n_tokens
             past = rc.num_tokens
@@ -304,7 +338,11 @@ class ModelRunner:
             ctx.host_positions_last.append(past + n - 1)
             ctx.host_state_slots.append(rc.slot)
             t0 += n
-        want_rows = np.asarray([r for i in range(len(entries)) for r in want_of_entry[i]], dtype=np.int32)
+        wanted = [r for i in range(len(entries)) for r in want_of_entry[i]]
+        n_wanted_real = len(wanted)
+        if n_fill and wanted:                  # the wanted rows are filled up the same way (with the first of them again)
+            wanted += [wanted[0]] * (_fill_to(len(wanted)) - len(wanted))
+        want_rows = np.asarray(wanted, dtype=np.int32)
 
         pieces = [token_ids, embed_row, positions, seq_of_token, slots.reshape(-1), token_of_seq, seq_starts,
                   state_slots, want_rows, tables.reshape(-1)]
@@ -320,11 +358,13 @@ class ModelRunner:
         per = n_seqs * max_pages
         ctx.block_tables = [tables_d[g * per: (g + 1) * per].view(n_seqs, max_pages) for g in range(n_groups)]
         ctx.n_tokens, ctx.n_seqs, ctx.n_decode, ctx.n_wanted = total, n_seqs, n_decode, int(want_rows.size)
+        ctx.n_wanted_real = n_wanted_real
         ctx.max_pages = max_pages
         ctx.bound_pages, ctx.granule_pages = bound_pages, granule_pages
         ctx.n_fed_back = sum(1 for e in ordered if e.fed_back is not None)
         if graphable:
-            ctx.graph_key = (n_decode, tuple(e.n_tokens for e in ordered[n_decode:]), max_pages, bound_pages, int(want_rows.size))
+            ctx.graph_key = (n_decode, tuple(e.n_tokens for e in ordered[n_decode - n_fill:]), max_pages, bound_pages,
+                             int(want_rows.size))
         if embed_chunks:
             ctx.embeds = torch.cat([c.to(device=self.device, dtype=self.dtype, non_blocking=True)
                                     for c in embed_chunks], dim=0).contiguous()
@@ -349,6 +389,8 @@ class ModelRunner:
         if ctx.n_fed_back:
             kernels.resolve_ids(ctx.token_ids, self.feedback, self.dtype)
         logits = self._forward(ctx)
+        if logits is not None and ctx.n_wanted_real < ctx.n_wanted:
+            logits = logits[: ctx.n_wanted_real]          # (the rest belongs to filler rows)
         self.finish(ordered)
         self.steps_run += 1
         self._status_host.copy_(self.status, non_blocking=True)

@@ -340,3 +340,52 @@ def test_abort_frees_at_once_and_disturbs_nobody(model_folders):
         assert ev.request_id == b
     assert engine.request(b).generated_token_ids == want and len(engine.request(a).generated_token_ids) == n_a
     assert engine.cache.free_pages() == [32] and engine.cache.slots.num_free == 2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_filler_rows_change_no_token_and_save_graphs(dtype, tmp_path):
+    """Requests that finish at different times make the number of single-token rows fall from 5 to 1; with
+    filler rows the steps are laid out for 8, 4, 2 and 1 rows, so fewer layouts are captured and more
+    steps replayed, and the tokens are those of an engine without fillers.  Free pages hold NaN, which
+    the fillers read (page 0 may be free) and which must reach nobody else."""
+    import shutil
+
+    from edgerag_b200 import Engine, SamplingParams
+
+    folder = plain.write_model_folder(tmp_path, plain.TINY_A, seed=3, std=0.2, dtype=getattr(torch, dtype))
+    try:
+        prompts = [helpers.random_sequence(512, 20 + 9 * i, 40 + i) for i in range(5)]
+        news = [6, 30, 14, 40, 22]
+        outs, stats = {}, {}
+        for fill in (False, True):
+            engine = Engine.from_pretrained(folder, dtype=dtype, block_size=16, num_blocks=40, max_batch_size=8, chunk_size=64,
+                                            max_prefills_per_step=5, cuda_graphs=True, pad_decodes=fill, poison_freed_pages=True)
+            ids = [engine.add_request(p, SamplingParams(max_new_tokens=n)) for p, n in zip(prompts, news)]
+            got = {i: [] for i in ids}
+            for ev in engine.stream():
+                got[ev.request_id].append(ev.token_id)
+            outs[fill] = [got[i] for i in ids]
+            stats[fill] = (len(engine.runner._graphs), engine.runner.graph_replays)
+            assert engine.cache.free_pages() == [40]
+        assert [len(o) for o in outs[True]] == news
+        if dtype == "float32":
+            assert outs[True] == outs[False]
+        else:
+            # bfloat16: the attention kernel's launch shape follows the number of rows, so the two engines may
+            # round differently; each follows the plain model wherever its top-2 margin is clear
+            cfg, weights = plain.read_config(folder), plain.read_weights(folder)
+            checked = 0
+            for fill in (False, True):
+                for prompt, out in zip(prompts, outs[fill]):
+                    logits = plain.forward(weights, cfg, list(prompt) + out[:-1])[len(prompt) - 1:]
+                    for got, row in zip(out, logits):
+                        top = torch.topk(row, 2).values
+                        if float(top[0] - top[1]) >= 0.05 * float(row.abs().max()):
+                            assert got == int(row.argmax())
+                            checked += 1
+            assert checked >= sum(news)
+        assert stats[True][0] <= stats[False][0] and stats[True][1] >= stats[False][1], stats
+        assert stats[True][1] > stats[False][1] or stats[True][0] < stats[False][0], stats
+    finally:
+        shutil.rmtree(tmp_path, ignore_errors=True)
