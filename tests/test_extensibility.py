@@ -216,3 +216,166 @@ def test_windowed_attention_layers_release_pages_behind_the_window(tmp_path):
     assert held[0] == 23 and held[1] <= (window + 3) // 4 + 1      # the windowed group kept only what is visible
     runner.release("w")
     assert engine.cache.free_pages() == [30, 30]
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """Two more parts defined here and registered from outside: a feed-forward that routes every token to
+    two of five small experts (router logits and gates in float32), and a position encoding that turns
+    neighbouring pairs of a head instead of its halves.  A plan mixes them with the framework's own parts
+    layer by layer (dense and routed feed-forwards, both encodings in one model); the model is built,
+    loaded and stepped in portions beside another request, in both element types, and its logits equal a
+    whole-sequence computation written out below.  Neither part is a model of anyone's."""
+    from edgerag_b200 import Engine
+    from edgerag_b200.config import register_architecture
+    from edgerag_b200.config.registry import architecture_of
+    from edgerag_b200.engine.step import StepEntry
+    from edgerag_b200.models.decoder import DecoderModel
+    from edgerag_b200.ops import kernels
+    from edgerag_b200.parts.base import (FeedForward, LayerCall, LayerSpec, ModelPlan, PartSpec, PositionEncoding, WeightSpec,
+                                         register_part)
+    from edgerag_b200.weights.loader import write_model_folder
+    import plain_llama as plain
+
+    h, nq, nkv, d, inter, vocab, layers = 40, 4, 2, 16, 56, 83, 3
+    experts, top, e_inter, theta = 5, 2, 24, 300.0
+
+    @register_part("ffn", "toy_routed")
+    class ToyRoutedFeedForward(FeedForward):
+        """y = sum over a token's two best experts of gate * down_e(relu(up_e(x))); gates: softmax over the two router logits."""
+
+        def __init__(self, hidden, experts, top, intermediate, dtype, device):
+            self.hidden, self.experts, self.top, self.intermediate = hidden, experts, top, intermediate
+            self.dtype, self.device = dtype, device
+
+        def weight_specs(self):
+            specs = [WeightSpec("router.weight", (self.experts, self.hidden), kind="keep")]
+            for e in range(self.experts):
+                specs += [WeightSpec(f"experts.{e}.up.weight", (self.intermediate, self.hidden)),
+                          WeightSpec(f"experts.{e}.down.weight", (self.hidden, self.intermediate))]
+            return specs
+
+        def load_weights(self, tensors):
+            self.router = tensors["router.weight"].to(device=self.device, dtype=torch.float32)
+            self.up = [tensors[f"experts.{e}.up.weight"].to(device=self.device, dtype=self.dtype) for e in range(self.experts)]
+            self.down = [tensors[f"experts.{e}.down.weight"].to(device=self.device, dtype=self.dtype) for e in range(self.experts)]
+
+        def forward(self, x, ctx):
+            logits = x.float() @ self.router.T                                    # float32 router
+            best, which = torch.topk(logits, self.top, dim=-1)
+            gates = torch.softmax(best, dim=-1)
+            y = torch.zeros((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
+            for e in range(self.experts):
+                weight = (gates * (which == e)).sum(dim=-1, keepdim=True)         # 0 for tokens that did not choose e
+                mid = torch.empty((x.shape[0], self.intermediate), dtype=self.dtype, device=x.device)
+                kernels.linear(x, self.up[e], mid)
+                out = torch.empty((x.shape[0], self.hidden), dtype=self.dtype, device=x.device)
+                kernels.linear(torch.relu(mid), self.down[e], out)
+                y += weight * out.float()
+            return y.to(self.dtype)
+
+    @register_part("position", "toy_pairs")
+    class ToyPairRotary(PositionEncoding):
+        """Turns the pairs (x[2i], x[2i + 1]) of every q and k head by position * theta^(-2i / D), then writes k and v to the cache."""
+
+        def __init__(self, head_dim, theta, dtype, device):
+            self.inv_freq = (1.0 / theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim)).to(device)
+
+        def apply_and_store(self, qkv, ctx, n_q_heads, n_kv_heads, head_dim, pages, slots):
+            n = qkv.shape[0]
+            angle = ctx.positions[:n].float()[:, None] * self.inv_freq[None]      # [n, D / 2]
+            cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+            turned = qkv[:, : (n_q_heads + n_kv_heads) * head_dim].float().view(n, n_q_heads + n_kv_heads, head_dim // 2, 2)
+            a, b = turned[..., 0], turned[..., 1]
+            both = torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).reshape(n, -1)
+            qkv[:, : both.shape[1]] = both.to(qkv.dtype)
+            if pages is not None:                                                 # rot_dim 0: the plain cache write
+                kernels.rope_cache_write(qkv, ctx.positions, None, n_q_heads, n_kv_heads, head_dim, 0, slots=slots,
+                                         k_pages=pages[0], v_pages=pages[1], page_size=ctx.page_size)
+
+    def make_plan(raw):
+        norm = lambda p: PartSpec("rmsnorm", {"size": h, "eps": 1e-5}, p)   # noqa: E731
+        dense = PartSpec("swiglu", {"hidden": h, "intermediate": inter}, "mlp.")
+        routed = PartSpec("toy_routed", {"hidden": h, "experts": experts, "top": top, "intermediate": e_inter}, "moe.")
+        pairs = PartSpec("toy_pairs", {"head_dim": d, "theta": theta})
+        halves = PartSpec("rope_halves", {"head_dim": d, "theta": theta})
+        specs = []
+        for i, (position, ffn) in enumerate([(pairs, dense), (halves, routed), (pairs, routed)]):
+            mixer = PartSpec("attention", {"hidden": h, "n_q_heads": nq, "n_kv_heads": nkv, "head_dim": d, "position": position}, "self_attn.")
+            specs.append(LayerSpec(f"layers.{i}.", PartSpec("prenorm"), norm("ln1."), mixer, norm("ln2."), ffn))
+        return ModelPlan(h, vocab, PartSpec("table", {"vocab": vocab, "hidden": h}, "embed_tokens."), specs,
+                         [LayerCall(i, i) for i in range(layers)], norm("norm."),
+                         PartSpec("linear", {"vocab": vocab, "hidden": h, "tied_to": None}, "lm_head."))
+
+    register_architecture("ToyRoutedForCausalLM", lambda raw, where: raw, make_plan)
+    raw = {"architectures": ["ToyRoutedForCausalLM"]}
+    specs = DecoderModel(architecture_of(raw).make_plan(raw), torch.float32, torch.device("cpu")).weight_specs()
+    folder = write_model_folder(tmp_path / "routed", raw, specs, seed=9, std=0.2, norm_jitter=0.1, dtype=torch.float32)
+    w = plain.read_weights(folder)
+
+    def attention_with(turn, x, a):
+        n = x.shape[0]
+        q = (x @ w[a + "q_proj.weight"].T).view(n, nq, d).transpose(0, 1)
+        k = (x @ w[a + "k_proj.weight"].T).view(n, nkv, d).transpose(0, 1)
+        v = (x @ w[a + "v_proj.weight"].T).view(n, nkv, d).transpose(0, 1)
+        return plain.attention_core(turn(q), turn(k), v, d ** -0.5) @ w[a + "o_proj.weight"].T
+
+    def whole(seq):
+        """The model on a whole sequence, float32, no cache: one expression per part."""
+        n = len(seq)
+        pos = torch.arange(n, dtype=torch.float32)
+        angle = pos[:, None] / theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d)[None]      # [n, D / 2]
+
+        def pairs(t):       # [heads, n, D]
+            a, b = t[..., 0::2], t[..., 1::2]
+            return torch.stack((a * angle.cos() - b * angle.sin(), a * angle.sin() + b * angle.cos()), dim=-1).reshape(t.shape)
+
+        cos, sin = plain.rope_tables(torch.arange(n), d, theta)
+        halves = lambda t: plain.apply_rope(t, cos, sin)   # noqa: E731
+        x = w["model.embed_tokens.weight"][torch.tensor(seq)]
+        for i, (turn, routed) in enumerate([(pairs, False), (halves, True), (pairs, True)]):
+            p = f"model.layers.{i}."
+            x = x + attention_with(turn, plain.rms_norm(x, w[p + "ln1.weight"], 1e-5), p + "self_attn.")
+            y = plain.rms_norm(x, w[p + "ln2.weight"], 1e-5)
+            if not routed:
+                m = p + "mlp."
+                x = x + plain.swiglu(y, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"])
+                continue
+            best, which = torch.topk(y @ w[p + "moe.router.weight"].T, top, dim=-1)
+            gates = torch.softmax(best, dim=-1)
+            out = torch.zeros_like(x)
+            for t in range(n):
+                for g, e in zip(gates[t], which[t]):
+                    m = f"{p}moe.experts.{int(e)}."
+                    out[t] += g * (torch.relu(y[t] @ w[m + "up.weight"].T) @ w[m + "down.weight"].T)
+            x = x + out
+        return plain.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["lm_head.weight"].T
+
+    seqs = {"x": torch.randint(0, vocab, (37,), generator=torch.Generator().manual_seed(1)).tolist(),
+            "y": torch.randint(0, vocab, (19,), generator=torch.Generator().manual_seed(2)).tolist()}
+    want = {k: whole(v) for k, v in seqs.items()}
+    assert len({int(e) for e in torch.topk(plain.rms_norm(w["model.embed_tokens.weight"], w["model.layers.1.ln2.weight"], 1e-5)
+                                          @ w["model.layers.1.moe.router.weight"].T, top, dim=-1).indices.flatten()}) >= 4
+    plan = [{"x": 9}, {"x": 2, "y": 6}, {"x": 1, "y": 1}, {"y": 12}, {"x": 25}]
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine.from_pretrained(folder, dtype=dtype, block_size=4, num_blocks=40, max_batch_size=3)
+        assert not engine.runner.graphs_enabled          # parts that do not declare themselves safe are never captured
+        runner = engine.runner
+        runner.admit("x"), runner.admit("y")
+        got, fed = {"x": [], "y": []}, {"x": 0, "y": 0}
+        for step in plan:
+            entries = [StepEntry(k, tokens=seqs[k][fed[k]: fed[k] + n], want=list(range(n))) for k, n in step.items()]
+            logits = runner.step(entries).cpu()
+            row = 0
+            for k, n in step.items():
+                got[k].append(logits[row: row + n].clone())
+                row += n
+                fed[k] += n
+        for k in seqs:
+            out = torch.cat(got[k])
+            if dtype == "float32":
+                torch.testing.assert_close(out, want[k], atol=2e-4, rtol=2e-4)
+            else:
+                scale = float(want[k].abs().max())
+                diff = (out - want[k]).abs()
+                # a token whose two best router logits lie close may go to another expert in bfloat16: judge the rest
+                assert float(diff.mean()) <= 0.01 * scale and float((diff.max(dim=1).values <= 0.03 * scale).float().mean()) >= 0.8
