@@ -48,3 +48,50 @@ def test_generation_with_every_page_size(name, config, std, dtype, tmp_path):
                 assert checked >= 12, "too few clear choices to judge by"
     finally:
         shutil.rmtree(tmp_path, ignore_errors=True)
+
+
+ODD = [
+    dict(hidden_size=100, num_attention_heads=5, num_key_value_heads=5, head_dim=16, intermediate_size=100, vocab_size=257),
+    dict(hidden_size=72, num_attention_heads=3, num_key_value_heads=1, head_dim=48, intermediate_size=250, vocab_size=1001),
+    dict(hidden_size=136, num_attention_heads=7, num_key_value_heads=7, head_dim=80, intermediate_size=136, vocab_size=300),
+    dict(hidden_size=200, num_attention_heads=6, num_key_value_heads=3, head_dim=112, intermediate_size=264, vocab_size=515),
+    dict(hidden_size=256, num_attention_heads=2, num_key_value_heads=2, head_dim=128, intermediate_size=512, vocab_size=999),
+    dict(hidden_size=192, num_attention_heads=9, num_key_value_heads=3, head_dim=64, intermediate_size=320, vocab_size=777),
+    dict(hidden_size=64, num_attention_heads=1, num_key_value_heads=1, head_dim=256, intermediate_size=96, vocab_size=130),
+    dict(hidden_size=90, num_attention_heads=10, num_key_value_heads=2, head_dim=32, intermediate_size=70, vocab_size=64),
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sizes", ODD, ids=lambda c: f"h{c['hidden_size']}-{c['num_attention_heads']}x{c['head_dim']}")
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_generation_with_sizes_that_are_no_powers_of_two(sizes, dtype, tmp_path):
+    """Widths, head counts, head sizes in steps of 16 up to 256, intermediate sizes and vocabularies that are
+    no powers of two (some no multiple of 8, where the vector kernels give way to the scalar ones and the
+    weight-streaming products to the library): every combination gives the plain model's tokens."""
+    import shutil
+
+    from edgerag_b200 import Engine, SamplingParams
+
+    config = dict(plain.TINY_A, **sizes, max_position_embeddings=1024)
+    folder = plain.write_model_folder(tmp_path, config, seed=sizes["hidden_size"], std=0.12, dtype=getattr(torch, dtype))
+    try:
+        cfg, weights = plain.read_config(folder), plain.read_weights(folder)
+        v = cfg["vocab"]
+        prompts = [[(7 * k + 3) % v for k in range(300)], [(11 * k + 5) % v for k in range(40)], [(13 * k + 1) % v for k in range(17)]]
+        margin = 0.05 if dtype == "bfloat16" else 1e-3
+        for graphs in (False, True):
+            engine = Engine.from_pretrained(folder, dtype=dtype, block_size=16, num_blocks=64, chunk_size=128, max_batch_size=4,
+                                            max_prefills_per_step=2, cuda_graphs=graphs, poison_freed_pages=True)
+            outs = engine.generate(prompts, SamplingParams(max_new_tokens=10))
+            checked = 0
+            for prompt, out in zip(prompts, outs):
+                logits = plain.forward(weights, cfg, list(prompt) + out[:-1])[len(prompt) - 1:]
+                for got, row in zip(out, logits):
+                    top = torch.topk(row, 2).values
+                    if float(top[0] - top[1]) >= margin * float(row.abs().max()):
+                        assert got == int(row.argmax()), f"{sizes}, graphs {graphs}"
+                        checked += 1
+            assert checked >= 10, "too few clear choices to judge by"
+    finally:
+        shutil.rmtree(tmp_path, ignore_errors=True)
