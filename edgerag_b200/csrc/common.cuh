@@ -91,6 +91,18 @@ __device__ __forceinline__ void load4(const float* p, float* out) {
   out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
 }
 
+// silu(g) * u in float.  Where the result is rounded to 16 bits (ERB_ELEM == 1) the exponential and the
+// division are the fast forms (relative error about 2^-21, far below that rounding); the 32-bit path keeps
+// the exact ones.  Every kernel that gates (the gate kernel, the gated epilogues of the products for few
+// rows) calls this, so that they agree to the bit.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+#if ERB_ELEM == 1
+  return __fdividef(g, 1.f + __expf(-g)) * u;
+#else
+  return g / (1.f + expf(-g)) * u;
+#endif
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -290,9 +290,75 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
   }
 }
 
-// Full rotation (rot_dim == head_dim, a multiple of 8): the angles of a token are computed once per
-// block into shared memory, every work item moves four consecutive elements of each half, and the
-// heads of a token are spread over gridDim.y blocks so that a few decode tokens still fill the GPU.
+// Sixteen bytes of consecutive elements as floats, and back (8 bfloat16 or 4 float).
+template <typename T> struct Wide;
+template <> struct Wide<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* v) { load4(p, v); }
+  static __device__ __forceinline__ void store(float* p, const float* v) { Pack4<float>::store(p, v); }
+};
+template <> struct Wide<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) { load8(p, v); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+};
+
+// Full rotation (rot_dim == head_dim, a multiple of 2 * Wide<T>::N): the angles of a token are computed
+// once per block into shared memory, every work item moves sixteen bytes of each half, and the heads of
+// a token are spread over gridDim.y blocks so that a few decode tokens still fill the GPU.
+template <typename T>
+__global__ void rope_cache_write_wide_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                             const float* __restrict__ inv_freq, const int* __restrict__ slots,
+                                             T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv,
+                                             int head_dim, int page_size, int write_kv) {
+  constexpr int N = Wide<T>::N;
+  extern __shared__ float trig[];            // cos[half], sin[half]
+  const int t = blockIdx.x;
+  const int half = head_dim / 2;
+  const float pos = (float)positions[t];
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], trig + half + j, trig + j);
+  const int slot = (write_kv && slots) ? slots[t] : -1;
+  __syncthreads();
+  chain_wait();
+  const int row_width = (nq + 2 * nkv) * head_dim;
+  T* row = qkv + (size_t)t * row_width;
+  const int page = slot >= 0 ? slot / page_size : 0;
+  const int offset = slot >= 0 ? slot % page_size : 0;
+  const int per_head = half / N;              // items per rotated head
+  const int rot_items = (nq + nkv) * per_head;
+  const int v_items = slot >= 0 ? nkv * head_dim / N : 0;
+  const int stride = gridDim.y * blockDim.x;
+  for (int w = blockIdx.y * blockDim.x + threadIdx.x; w < rot_items + v_items; w += stride) {
+    if (w < rot_items) {
+      const int head = w / per_head, j = (w % per_head) * N;
+      if (head >= nq && slot < 0) continue;
+      T* x = row + (size_t)head * head_dim;
+      float a[N], b[N], lo[N], hi[N];
+      Wide<T>::load(x + j, a);
+      Wide<T>::load(x + j + half, b);
+#pragma unroll
+      for (int i = 0; i < N; ++i) rotate_pair(a[i], b[i], trig[j + i], trig[half + j + i], lo[i], hi[i]);
+      T* dst = x;
+      if (head >= nq) dst = k_pages + (((size_t)page * nkv + (head - nq)) * page_size + offset) * head_dim;
+      Wide<T>::store(dst + j, lo);
+      Wide<T>::store(dst + j + half, hi);
+    } else {
+      const int i = (w - rot_items) * N;
+      const int kvh = i / head_dim, e = i % head_dim;
+      float v[N];
+      Wide<T>::load(row + (size_t)(nq + nkv) * head_dim + i, v);
+      Wide<T>::store(v_pages + (((size_t)page * nkv + kvh) * page_size + offset) * head_dim + e, v);
+    }
+  }
+}
+
+// The same with eight-byte accesses (four elements), for head sizes that are a multiple of 8 only.
 template <typename T>
 __global__ void rope_cache_write_vec4_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                              const float* __restrict__ inv_freq, const int* __restrict__ slots,
@@ -342,6 +408,11 @@ __global__ void rope_cache_write_vec4_kernel(T* __restrict__ qkv, const int* __r
   }
 }
 
+// Whether every row of qkv and every head inside it starts on a 16-byte boundary.
+static bool row_bytes_16(int nq, int nkv, int head_dim, size_t elem) {
+  return ((size_t)(nq + 2 * nkv) * head_dim * elem) % 16 == 0 && ((size_t)head_dim * elem) % 32 == 0;
+}
+
 ERB_EXPORT int erb_rope_cache_write(void* qkv, const int* positions, const float* inv_freq,
                                     const int* slots, void* k_pages, void* v_pages, int n_tokens,
                                     int nq, int nkv, int head_dim, int rot_dim, int page_size,
@@ -356,11 +427,18 @@ ERB_EXPORT int erb_rope_cache_write(void* qkv, const int* positions, const float
   const int threads = work >= 512 ? 256 : 128;
   if (rot_dim == head_dim && head_dim % 8 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)k_pages & 15) &&
       !((uintptr_t)v_pages & 15)) {
-    const int items = (nq + nkv) * head_dim / 8 + nkv * head_dim / 4;
+    const bool wide = head_dim % (2 * Wide<elem_t>::N) == 0 && row_bytes_16(nq, nkv, head_dim, sizeof(elem_t));
+    const int per = wide ? Wide<elem_t>::N : 4;
+    const int items = (nq + nkv) * head_dim / (2 * per) + nkv * head_dim / per;
     int y = (items + 127) / 128;
     const int want = (sm_count() * 8 + n_tokens - 1) / n_tokens;      // enough blocks for every SM
     if (y > want) y = want;
     if (y < 1) y = 1;
+    if (wide) {
+      launch_chained(rope_cache_write_wide_kernel<elem_t>, dim3(dim3(n_tokens, y)), dim3(128), head_dim * sizeof(float), (cudaStream_t)stream,
+          (elem_t*)qkv, positions, inv_freq, slots, (elem_t*)k_pages, (elem_t*)v_pages, nq, nkv, head_dim, page_size, write_kv);
+      return check_launch("rope_cache_write");
+    }
     launch_chained(rope_cache_write_vec4_kernel<elem_t>, dim3(dim3(n_tokens, y)), dim3(128), head_dim * sizeof(float), (cudaStream_t)stream, 
         (elem_t*)qkv, positions, inv_freq, slots, (elem_t*)k_pages, (elem_t*)v_pages, nq, nkv, head_dim, page_size,
         write_kv);
@@ -383,8 +461,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   const int i = (int)(idx % inter);
   const T* row = gate_up + t * 2 * (size_t)inter;
   const float g = Elem<T>::load(row + i), u = Elem<T>::load(row + inter + i);
-  const float act = g / (1.f + expf(-g));
-  Elem<T>::store(out + idx, act * u);
+  Elem<T>::store(out + idx, silu_mul(g, u));
 }
 
 template <typename T> struct Vec16;   // 16-byte groups
@@ -416,7 +493,7 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__
   Vec16<T>::load(row + i, g);
   Vec16<T>::load(row + inter + i, u);
 #pragma unroll
-  for (int j = 0; j < N; ++j) g[j] = g[j] / (1.f + expf(-g[j])) * u[j];
+  for (int j = 0; j < N; ++j) g[j] = silu_mul(g[j], u[j]);
   Vec16<T>::store(out + t * (size_t)inter + i, g);
 }
 

@@ -276,7 +276,7 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
       v1 = __bfloat162float(__float2bfloat16_rn(v1));
       if constexpr (GLU) {
         const int n = n0 + rr;
-        if (n < N) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v0 / (1.f + expf(-v0)) * v1);
+        if (n < N) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(silu_mul(v0, v1));
       } else {
         const int D = ra.head_dim, half = D / 2;
         const int slot = ra.slots[m];

@@ -250,7 +250,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (n >= N) continue;
       const float g = __bfloat162float(__float2bfloat16_rn(sums[m * kTileN + e]));
       const float u = __bfloat162float(__float2bfloat16_rn(sums[m * kTileN + kTileN / 2 + e]));
-      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(silu_mul(g, u));
     }
   } else {
     // rotary halves on q and k heads (a thread takes a pair), cache write of k and v
