@@ -107,14 +107,17 @@ template <> struct Pack4<__nv_bfloat16> {
 // threads: a block of VT / R threads keeps R partial sums per thread, one per virtual thread it
 // stands for.  So the launch may use fewer, busier threads for many rows and more threads for the
 // few rows of a decode step, and a row's result does not depend on which.
-template <typename T, int R>
-__global__ void __launch_bounds__(512, 4)   // 32 registers: the SM's 2,048 threads stay resident
+// REGS: the row fits one pass (hidden_size <= 4 * VT), so a thread keeps its elements in registers between
+// the sum and the scaling instead of parking the row in shared memory; the sums are the same.
+template <typename T, int R, bool REGS>
+__global__ void __launch_bounds__(512, (REGS && R > 1) ? 2 : 4)   // (32 registers where 2,048 threads stay resident)
 add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
                                         int write_back) {
   extern __shared__ float row_cache[];
-  float* scratch = row_cache + hidden_size;
+  float* scratch = REGS ? row_cache : row_cache + hidden_size;
+  float keep[REGS ? R : 1][4];
   const int o = blockIdx.x;
   const int r = rows ? rows[o] : o;            // the step's metadata: not written by the kernel before
   float* h = hidden + (size_t)r * hidden_size;
@@ -142,7 +145,12 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
         for (int j = 0; j < 4; ++j) v[j] += dv[j];
         if (write_back) *reinterpret_cast<float4*>(h + i) = make_float4(v[0], v[1], v[2], v[3]);
       }
-      *reinterpret_cast<float4*>(row_cache + i) = make_float4(v[0], v[1], v[2], v[3]);
+      if constexpr (REGS) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) keep[q][j] = v[j];
+      } else {
+        *reinterpret_cast<float4*>(row_cache + i) = make_float4(v[0], v[1], v[2], v[3]);
+      }
       ss[q] += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
     }
   }
@@ -159,6 +167,24 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
   const float total = warp_sum(lane < warps * R ? scratch[lane] : 0.f);
   const float rs = rsqrtf(total / (float)hidden_size + eps);
   T* y = out + (size_t)o * hidden_size;
+  if constexpr (REGS) {
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const int i = (threadIdx.x + q * threads) * 4;
+      if (i >= hidden_size) continue;
+      float w[4], v[4];
+      if (q == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = w_first[j];
+      } else {
+        load4(weight + i, w);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = w[j] * Elem<T>::round(keep[q][j] * rs);
+      Pack4<T>::store(y + i, v);
+    }
+    return;
+  }
   for (int i = threadIdx.x * 4; i < hidden_size; i += threads * 4) {
     float v[4], w[4];
     load4(row_cache + i, v);
@@ -194,16 +220,24 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
   if (vec) {
     // many rows of 2048 and more: half the threads, two virtual threads each (same sums, see the kernel)
     const bool halve = threads == 512 && n_rows > 64;
-    if (smem > 48 * 1024) {
-      cudaError_t e = halve ? cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                            : cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const bool one_pass = hidden_size <= threads * 4;     // a row fits the registers of its block
+    if (smem > 48 * 1024 && !one_pass) {
+      cudaError_t e = halve ? cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                            : cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "add_rmsnorm: %s", cudaGetErrorString(e));
     }
-    if (halve)
-      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2>, dim3(n_rows), dim3(256), smem, (cudaStream_t)stream, (float*)hidden,
+    const size_t small = 32 * sizeof(float);
+    if (halve && one_pass)
+      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2, true>, dim3(n_rows), dim3(256), small, (cudaStream_t)stream, (float*)hidden,
+          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+    else if (halve)
+      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2, false>, dim3(n_rows), dim3(256), smem, (cudaStream_t)stream, (float*)hidden,
+          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+    else if (one_pass)
+      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, true>, dim3(n_rows), dim3(threads), small, (cudaStream_t)stream, (float*)hidden,
           (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
     else
-      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
+      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, false>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
           (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
   } else {
     launch_chained(add_rmsnorm_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
