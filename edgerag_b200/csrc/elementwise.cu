@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(512, (REGS && R > 1) ? 2 : 4)   // (32 registe
 add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
-                                        int write_back) {
+                                        int write_back, int settled) {
   extern __shared__ float row_cache[];
   float* scratch = REGS ? row_cache : row_cache + hidden_size;
   float keep[REGS ? R : 1][4];
@@ -127,6 +127,17 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
   const int i_first = threadIdx.x * 4;
   float w_first[4] = {0.f, 0.f, 0.f, 0.f};
   if (i_first < hidden_size) load4(weight + i_first, w_first);
+  // `settled`: the residual stream was last written two or more kernels ago (the kernel just before this
+  // one wrote `delta` only), so its rows may be read while that kernel is still running.
+  if constexpr (REGS) {
+    if (settled) {
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        const int i = (threadIdx.x + q * threads) * 4;
+        if (i < hidden_size) load4(h + i, keep[q]);
+      }
+    }
+  }
   chain_wait();
   float ss[R];
 #pragma unroll
@@ -137,7 +148,12 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
       const int i = base + (threadIdx.x + q * threads) * 4;
       if (i >= hidden_size) continue;
       float v[4];
-      load4(h + i, v);
+      if (REGS && settled) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = keep[q][j];
+      } else {
+        load4(h + i, v);
+      }
       if (d) {
         float dv[4];
         Pack4<T>::load(d + i, dv);
@@ -202,7 +218,7 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
 
 ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* weight, void* out,
                                const int* rows, int n_rows, int hidden_size, float eps, int write_back,
-                               void* stream) {
+                               int settled, void* stream) {
   if (n_rows <= 0) return ERB_OK;
   const size_t smem = (size_t)(hidden_size + 32) * sizeof(float);
   if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "add_rmsnorm: hidden_size %d too large", hidden_size);
@@ -229,16 +245,16 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
     const size_t small = 32 * sizeof(float);
     if (halve && one_pass)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2, true>, dim3(n_rows), dim3(256), small, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
     else if (halve)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2, false>, dim3(n_rows), dim3(256), smem, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
     else if (one_pass)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, true>, dim3(n_rows), dim3(threads), small, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
     else
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, false>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
   } else {
     launch_chained(add_rmsnorm_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
         (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);

@@ -11,6 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..cache.manager import CacheLayout, KVGroupSpec, StateSpec
+from ..ops import kernels
 from ..parts.base import _REGISTRY, LayerCall, ModelPlan, Part, WeightSpec, build_part
 
 
@@ -108,17 +109,20 @@ class DecoderModel:
         n = ctx.n_tokens
         hidden = ctx.buf("model.hidden", (n, self.hidden_size), torch.float32)
         self.embedding.forward(ctx, hidden)
+        ctx.stream_written = kernels.launches()      # (the embedding wrote the residual stream: see the block)
         delta = None
         for call in self.schedule:
+            before = ctx.stream_written
             delta = self.blocks[call.layer].forward(hidden, delta, ctx, call)
+            if ctx.stream_written == before:      # a block that keeps no account of its writes to the stream:
+                ctx.stream_written = float("inf")  # nobody may assume that the stream has settled
         w = ctx.n_wanted
         if w == 0:
             return None
-        from ..ops import kernels
-
         y = ctx.buf("model.final", (w, self.hidden_size), self.dtype)
         if self.final_norm is not None:
-            self.final_norm.forward(hidden, y, delta, rows=ctx.want_rows, write_back=False)
+            self.final_norm.forward(hidden, y, delta, rows=ctx.want_rows, write_back=False,
+                                    settled=kernels.launches() > ctx.stream_written)
         else:
             if delta is not None:
                 kernels.residual_add(hidden, delta)

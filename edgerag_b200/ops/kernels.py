@@ -25,7 +25,7 @@ _ELEM = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
 _SIGNATURES = {
     "erb_embed_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                        c_void_p, c_void_p],
-    "erb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+    "erb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int,
                         c_void_p],
     "erb_residual_add": [c_void_p, c_void_p, c_longlong, c_void_p],
     "erb_rope_cache_write": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -67,6 +67,11 @@ launch_counts = {"own": 0, "library": 0}
 _LAUNCHES = {"erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
 TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
+
+
+def launches() -> int:
+    """Kernels launched through this module so far (this package's own and the library's)."""
+    return launch_counts["own"] + launch_counts["library"]
 
 
 def _fn(library: str, elem: str | None, name: str):
@@ -142,8 +147,10 @@ def embed_rows(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, sta
 
 def add_rmsnorm(hidden: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
                 delta: torch.Tensor | None = None, rows: torch.Tensor | None = None,
-                write_back: bool = True) -> None:
-    """out = weight * round(rmsnorm(hidden (+ delta))); hidden += delta in place when write_back."""
+                write_back: bool = True, settled: bool = False) -> None:
+    """out = weight * round(rmsnorm(hidden (+ delta))); hidden += delta in place when write_back.
+    ``settled``: ``hidden`` was last written two or more launches ago (the launch just before this one
+    wrote ``delta`` at most), so the kernel may read it while that launch is still running."""
     _need(hidden, "hidden", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
     _need(delta, "delta", out.dtype); _need(rows, "rows", torch.int32)
     h = hidden.shape[1]
@@ -155,7 +162,7 @@ def add_rmsnorm(hidden: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, e
     if rows is not None and rows.numel() < n:
         raise KernelError("add_rmsnorm: fewer row indices than output rows")
     _call(_fn("elementwise", _elem(out), "erb_add_rmsnorm"), hidden.data_ptr(), _ptr(delta), weight.data_ptr(),
-          out.data_ptr(), _ptr(rows), n, h, float(eps), int(write_back and rows is None), _stream())
+          out.data_ptr(), _ptr(rows), n, h, float(eps), int(write_back and rows is None), int(bool(settled)), _stream())
 
 
 def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:

@@ -115,9 +115,11 @@ class Part:
 
 class Norm(Part):
     def forward(self, hidden: torch.Tensor, out: torch.Tensor, delta: torch.Tensor | None = None,
-                rows: torch.Tensor | None = None, write_back: bool = True) -> None:
+                rows: torch.Tensor | None = None, write_back: bool = True, settled: bool = False) -> None:
         """``hidden`` (float32, the residual stream) gets ``delta`` added in place when given and
-        ``write_back``; ``out`` receives the normed rows (all rows, or ``rows`` of them)."""
+        ``write_back``; ``out`` receives the normed rows (all rows, or ``rows`` of them).  ``settled`` is a
+        hint that a norm may ignore: the caller vouches that ``hidden`` was not written by the kernel
+        launched just before this call (only ``delta`` was), so it may be read while that kernel runs."""
         raise NotImplementedError
 
 

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import kernels
 from .base import Block, FeedForward, LayerCall, Mixer, Norm, register_part
 
 
@@ -26,7 +27,14 @@ class PreNormBlock(Block):
     def forward(self, hidden: torch.Tensor, delta: torch.Tensor | None, ctx, call: LayerCall) -> torch.Tensor:
         n = hidden.shape[0]
         x = ctx.buf("block.normed", (n, self.hidden), self.dtype)
-        self.norm1.forward(hidden, x, delta)          # hidden += delta; x = norm1(hidden)
+        # A norm may read the stream while the kernel before it still runs if that kernel did not write the
+        # stream: true when at least one kernel of this package has been launched since the stream's last
+        # writer (`ctx.stream_written`, the launch count right after it).
+        settled = lambda: kernels.launches() > getattr(ctx, "stream_written", float("inf"))   # noqa: E731
+        self.norm1.forward(hidden, x, delta, settled=settled())   # hidden += delta; x = norm1(hidden)
+        if delta is not None:
+            ctx.stream_written = kernels.launches()
         mixed = self.mixer.forward(x, ctx, call)
-        self.norm2.forward(hidden, x, mixed)          # hidden += mixed; x = norm2(hidden)
+        self.norm2.forward(hidden, x, mixed, settled=settled())   # hidden += mixed; x = norm2(hidden)
+        ctx.stream_written = kernels.launches()
         return self.ffn.forward(x, ctx)               # added by whichever norm comes next

@@ -31,5 +31,5 @@ class RMSNorm(Norm):
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].to(device=self.device, dtype=torch.float32).contiguous()
 
-    def forward(self, hidden, out, delta=None, rows=None, write_back=True) -> None:
-        kernels.add_rmsnorm(hidden, self.weight, out, self.eps, delta=delta, rows=rows, write_back=write_back)
+    def forward(self, hidden, out, delta=None, rows=None, write_back=True, settled=False) -> None:
+        kernels.add_rmsnorm(hidden, self.weight, out, self.eps, delta=delta, rows=rows, write_back=write_back, settled=settled)
