@@ -26,6 +26,11 @@ struct Plan {
   cublasLtMatrixLayout_t a = nullptr, b = nullptr, c = nullptr;
   cublasLtMatmulAlgo_t algo;
   size_t workspace = 0;
+  // other algorithms the library proposed for this shape (the first is its own first choice), to be
+  // timed against each other on the first call that is not inside a stream capture
+  cublasLtMatmulHeuristicResult_t candidates[8];
+  int n_candidates = 0;
+  bool tuned = false;
 };
 
 using Key = std::tuple<int, int, int, int, int, int, int, int, size_t>;
@@ -78,16 +83,62 @@ int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f
   LT_CHECK(cublasLtMatmulPreferenceCreate(&pref));
   LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws_bytes,
                                                 sizeof(ws_bytes)));
-  cublasLtMatmulHeuristicResult_t result;
   int found = 0;
-  cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(g_handle, p.op, p.a, p.b, p.c, p.c, pref, 1, &result, &found);
+  cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(g_handle, p.op, p.a, p.b, p.c, p.c, pref, 8, p.candidates, &found);
   cublasLtMatmulPreferenceDestroy(pref);
   if (st != CUBLAS_STATUS_SUCCESS || found == 0)
     return fail(ERB_ERR_UNSUPPORTED, "linear: no cuBLASLt algorithm for M=%d N=%d K=%d lda=%d ldw=%d ldo=%d (%s)",
                 M, N, K, lda, ldw, ldo, status_name(st));
-  p.algo = result.algo;
-  p.workspace = result.workspaceSize;
+  p.n_candidates = found;
+  p.algo = p.candidates[0].algo;
+  p.workspace = p.candidates[0].workspaceSize;
   return ERB_OK;
+}
+
+bool tuning_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("EDGERAG_B200_NO_TUNE");
+    return !(v && v[0] == '1');
+  }();
+  return on;
+}
+
+// The library's first choice is not always its fastest algorithm for a shape (few rows against a long k:
+// 13 us where another of its proposals takes 8).  On a plan's first use outside a stream capture every
+// proposal runs a few times on the caller's operands (each writes the same product to `out`), timed
+// with events, and the fastest stays.  One choice per shape and process.
+void tune_plan(Plan& p, const void* a, const void* w, void* out, void* workspace, size_t ws, cudaStream_t stream) {
+  p.tuned = true;
+  if (p.n_candidates < 2 || !tuning_enabled()) return;
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+    p.tuned = false;        // (not now: the next call outside a capture decides)
+    return;
+  }
+  cudaEvent_t t0, t1;
+  if (cudaEventCreate(&t0) != cudaSuccess) return;
+  if (cudaEventCreate(&t1) != cudaSuccess) { cudaEventDestroy(t0); return; }
+  const float alpha = 1.f, beta = 0.f;
+  float best = 1e30f;
+  int best_i = 0;
+  for (int i = 0; i < p.n_candidates; ++i) {
+    const cublasLtMatmulHeuristicResult_t& c = p.candidates[i];
+    if (c.state != CUBLAS_STATUS_SUCCESS || c.workspaceSize > ws) continue;
+    bool ok = true;
+    for (int r = 0; r < 4 && ok; ++r) {     // one to warm up, three timed
+      if (r == 1) cudaEventRecord(t0, stream);
+      ok = cublasLtMatmul(g_handle, p.op, &alpha, w, p.a, a, p.b, &beta, out, p.c, out, p.c, &c.algo, workspace, ws,
+                          stream) == CUBLAS_STATUS_SUCCESS;
+    }
+    cudaEventRecord(t1, stream);
+    if (cudaEventSynchronize(t1) != cudaSuccess || !ok) continue;
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, t0, t1) == cudaSuccess && ms < best) { best = ms; best_i = i; }
+  }
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  p.algo = p.candidates[best_i].algo;
+  p.workspace = p.candidates[best_i].workspaceSize;
 }
 
 }  // namespace
@@ -110,7 +161,8 @@ ERB_EXPORT int erb_linear(const void* a, const void* w, void* out, int M, int N,
     if (rc) return rc;
     it = g_plans.emplace(key, p).first;
   }
-  const Plan& p = it->second;
+  Plan& p = it->second;
+  if (!p.tuned && !accumulate) tune_plan(p, a, w, out, workspace, ws, (cudaStream_t)stream);
   const float alpha = 1.f, beta = accumulate ? 1.f : 0.f;
   LT_CHECK(cublasLtMatmul(g_handle, p.op, &alpha, w, p.a, a, p.b, &beta, out, p.c, out, p.c, &p.algo,
                           workspace, ws, (cudaStream_t)stream));
