@@ -240,19 +240,33 @@ def _workspace(device: torch.device) -> torch.Tensor:
 
 
 _set_status_word = None
+_status_word: torch.Tensor | None = None     # where the tensor-core weight-streaming kernel reports
+_status_word_told: int | None = None         # ... and what the library was last told
 
 
 def linear_status_word(status: torch.Tensor | None) -> None:
     """Name the device word (int32) to which the TMA + tcgen05 weight-streaming kernel reports a wait
-    that ran out (code 4000000 + block).  Kept until named again."""
-    global _set_status_word
+    that ran out (code 4000000 + block).  Kept until named again.  The library itself is told when it
+    is next used (a model that never brings 17 to 64 rows to a large product never builds it)."""
+    global _status_word
     if status is not None:
         _need(status, "status", torch.int32)
-    if _set_status_word is None:
-        _set_status_word = native.load("linear_tc", None).erb_linear_tc_set_status_word
-        _set_status_word.argtypes = [c_void_p]
-        _set_status_word.restype = c_int
-    _set_status_word(_ptr(status))
+    _status_word = status
+
+
+def _fn_tc(name: str):
+    """A function of the tensor-core weight-streaming library, which first hears of the status word if it has changed."""
+    global _set_status_word, _status_word_told
+    fn = _fn("linear_tc", None, name)
+    told = None if _status_word is None else _status_word.data_ptr()
+    if told != _status_word_told:
+        if _set_status_word is None:
+            _set_status_word = fn._erb_lib.erb_linear_tc_set_status_word
+            _set_status_word.argtypes = [c_void_p]
+            _set_status_word.restype = c_int
+        _set_status_word(told)
+        _status_word_told = told
+    return fn
 
 
 def linear_few_rows_supported(a: torch.Tensor, weight: torch.Tensor, lda: int) -> bool:
@@ -290,7 +304,7 @@ def linear_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("linear_tc: shapes or strides disagree")
     if out.dtype not in (torch.bfloat16, torch.float32) or not linear_few_rows_supported(a, weight, lda):
         raise KernelError("linear_tc: operands not supported")
-    _call(_fn("linear_tc", None, "erb_linear_tc"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, lda, k, ldo,
+    _call(_fn_tc("erb_linear_tc"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, lda, k, ldo,
           int(out.dtype == torch.float32), _stream())
 
 
@@ -304,7 +318,7 @@ def linear_tc_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> N
         raise KernelError("linear_tc_glu: shapes, strides or operands not supported")
     lda = a.stride(0) if m > 1 else max(k, a.stride(0))
     ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
-    _call(_fn("linear_tc", None, "erb_linear_tc_glu"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, lda, k, ldo,
+    _call(_fn_tc("erb_linear_tc_glu"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, lda, k, ldo,
           _stream())
 
 
@@ -325,7 +339,7 @@ def linear_tc_rope_store(a: torch.Tensor, weight: torch.Tensor, qkv: torch.Tenso
         raise KernelError("linear_tc_rope_store: shapes, strides or operands not supported")
     lda = a.stride(0) if m > 1 else max(k, a.stride(0))
     ldo = qkv.stride(0) if m > 1 else max(width, qkv.stride(0))
-    _call(_fn("linear_tc", None, "erb_linear_tc_rope"), a.data_ptr(), weight.data_ptr(), qkv.data_ptr(), m, k, lda, k, ldo,
+    _call(_fn_tc("erb_linear_tc_rope"), a.data_ptr(), weight.data_ptr(), qkv.data_ptr(), m, k, lda, k, ldo,
           n_q_heads, n_kv_heads, head_dim, positions.data_ptr(), inv_freq.data_ptr(), slots.data_ptr(),
           k_pages.data_ptr(), v_pages.data_ptr(), page_size, _stream())
 
@@ -416,7 +430,7 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate:
                   lda, k, ldo, int(out.dtype == torch.float32), _stream())
             return
         if n >= 128 * 2 * _sms(a.device):
-            _call(_fn("linear_tc", None, "erb_linear_tc"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+            _call(_fn_tc("erb_linear_tc"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
                   lda, k, ldo, int(out.dtype == torch.float32), _stream())
             return
     ws = _workspace(a.device)
