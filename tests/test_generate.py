@@ -361,7 +361,10 @@ def test_filler_rows_change_no_token_and_save_graphs(dtype, tmp_path):
         for fill in (False, True):
             engine = Engine.from_pretrained(folder, dtype=dtype, block_size=16, num_blocks=40, max_batch_size=8, chunk_size=64,
                                             max_prefills_per_step=5, cuda_graphs=True, pad_decodes=fill, poison_freed_pages=True)
-            ids = [engine.add_request(p, SamplingParams(max_new_tokens=n)) for p, n in zip(prompts, news)]
+            # (two of the requests sample with a temperature: their draws depend on the request and the token's
+            # index only, so the filler rows must not shift them either)
+            ids = [engine.add_request(p, SamplingParams(max_new_tokens=n, temperature=0.8 if i % 2 else 0.0, seed=17 + i))
+                   for i, (p, n) in enumerate(zip(prompts, news))]
             got = {i: [] for i in ids}
             for ev in engine.stream():
                 got[ev.request_id].append(ev.token_id)
@@ -377,14 +380,16 @@ def test_filler_rows_change_no_token_and_save_graphs(dtype, tmp_path):
             cfg, weights = plain.read_config(folder), plain.read_weights(folder)
             checked = 0
             for fill in (False, True):
-                for prompt, out in zip(prompts, outs[fill]):
+                for i, (prompt, out) in enumerate(zip(prompts, outs[fill])):
+                    if i % 2:
+                        continue        # (sampled: judged in float32 only, where the two engines must agree)
                     logits = plain.forward(weights, cfg, list(prompt) + out[:-1])[len(prompt) - 1:]
                     for got, row in zip(out, logits):
                         top = torch.topk(row, 2).values
                         if float(top[0] - top[1]) >= 0.05 * float(row.abs().max()):
                             assert got == int(row.argmax())
                             checked += 1
-            assert checked >= sum(news)
+            assert checked >= sum(news[::2])
         assert stats[True][0] <= stats[False][0] and stats[True][1] >= stats[False][1], stats
         assert stats[True][1] > stats[False][1] or stats[True][0] < stats[False][0], stats
     finally:
