@@ -31,6 +31,7 @@ struct Plan {
   cublasLtMatmulHeuristicResult_t candidates[8];
   int n_candidates = 0;
   bool tuned = false;
+  int uses = 0;        // calls outside a stream capture so far
 };
 
 using Key = std::tuple<int, int, int, int, int, int, int, int, size_t>;
@@ -60,6 +61,23 @@ const char* status_name(cublasStatus_t s) {
       return fail(ERB_ERR_CUDA, "linear: %s -> %s", #expr, status_name(st__));                 \
   } while (0)
 
+bool tuning_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("EDGERAG_B200_NO_TUNE");
+    return !(v && v[0] == '1');
+  }();
+  return on;
+}
+
+// The library's first choice is not always its fastest algorithm for a shape (the products of a 2,048-token
+// portion: 5 % of the step).  A shape with 1,024 rows or more that keeps coming back is worth a look: on its
+// third use outside a stream capture every proposal runs a few times on the caller's operands (each
+// writes the same product to `out`), timed with events, and the fastest stays.  One choice per shape and
+// process.  Not below 1,024 rows: the proposals are timed back to back, with the weights in L2, which for
+// the 513 to 576 rows of a serving step picked algorithms that were slower inside the step (weights from
+// DRAM) than the library's first choice, and the odd row counts of such steps would each pay for a trial.
+constexpr int kTuneFromRows = 1024, kTuneAtUse = 3;
+
 int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f32, int accumulate,
               size_t ws_bytes) {
 #if ERB_ELEM == 0
@@ -84,7 +102,8 @@ int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f
   LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws_bytes,
                                                 sizeof(ws_bytes)));
   int found = 0;
-  cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(g_handle, p.op, p.a, p.b, p.c, p.c, pref, 8, p.candidates, &found);
+  const int want = (M >= kTuneFromRows && tuning_enabled()) ? 8 : 1;   // more than one only where they get timed
+  cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(g_handle, p.op, p.a, p.b, p.c, p.c, pref, want, p.candidates, &found);
   cublasLtMatmulPreferenceDestroy(pref);
   if (st != CUBLAS_STATUS_SUCCESS || found == 0)
     return fail(ERB_ERR_UNSUPPORTED, "linear: no cuBLASLt algorithm for M=%d N=%d K=%d lda=%d ldw=%d ldo=%d (%s)",
@@ -95,26 +114,12 @@ int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f
   return ERB_OK;
 }
 
-bool tuning_enabled() {
-  static const bool on = [] {
-    const char* v = getenv("EDGERAG_B200_NO_TUNE");
-    return !(v && v[0] == '1');
-  }();
-  return on;
-}
-
-// The library's first choice is not always its fastest algorithm for a shape (few rows against a long k:
-// 13 us where another of its proposals takes 8).  On a plan's first use outside a stream capture every
-// proposal runs a few times on the caller's operands (each writes the same product to `out`), timed
-// with events, and the fastest stays.  One choice per shape and process.
-void tune_plan(Plan& p, const void* a, const void* w, void* out, void* workspace, size_t ws, cudaStream_t stream) {
-  p.tuned = true;
-  if (p.n_candidates < 2 || !tuning_enabled()) return;
+void tune_plan(Plan& p, int M, const void* a, const void* w, void* out, void* workspace, size_t ws, cudaStream_t stream) {
+  if (p.n_candidates < 2 || M < kTuneFromRows || !tuning_enabled()) { p.tuned = true; return; }
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
-    p.tuned = false;        // (not now: the next call outside a capture decides)
-    return;
-  }
+  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) return;
+  if (++p.uses < kTuneAtUse) return;
+  p.tuned = true;
   cudaEvent_t t0, t1;
   if (cudaEventCreate(&t0) != cudaSuccess) return;
   if (cudaEventCreate(&t1) != cudaSuccess) { cudaEventDestroy(t0); return; }
@@ -162,7 +167,7 @@ ERB_EXPORT int erb_linear(const void* a, const void* w, void* out, int M, int N,
     it = g_plans.emplace(key, p).first;
   }
   Plan& p = it->second;
-  if (!p.tuned && !accumulate) tune_plan(p, a, w, out, workspace, ws, (cudaStream_t)stream);
+  if (!p.tuned && !accumulate) tune_plan(p, M, a, w, out, workspace, ws, (cudaStream_t)stream);
   const float alpha = 1.f, beta = accumulate ? 1.f : 0.f;
   LT_CHECK(cublasLtMatmul(g_handle, p.op, &alpha, w, p.a, a, p.b, &beta, out, p.c, out, p.c, &p.algo,
                           workspace, ws, (cudaStream_t)stream));
