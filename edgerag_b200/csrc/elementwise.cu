@@ -47,6 +47,9 @@ ERB_EXPORT int erb_embed_rows(void* hidden, const void* table, const void* embed
 // ---------------------------------------------------------------------------------------------
 // Residual add + RMSNorm.
 //   r = hidden[row] (+ delta[row])            in float, stored back when `write_back`
+// The update may also come as `n_parts` float arrays of partial sums, `part_stride` floats apart (a
+// product whose k was split over blocks): delta = round_T(((p0 + p1) + p2) + ...), added in float in that
+// order and rounded to T once, as if the product had been stored in T like every other update.
 //   y = weight * round_T( r * rsqrt(mean(r^2) + eps) )     rounded to T once more
 // The statistics, the scale and the residual sum are float; the cast to T comes before the
 // weight multiply, as in the reference's RMSNorm.  `rows`, when given, selects the rows of
@@ -54,6 +57,7 @@ ERB_EXPORT int erb_embed_rows(void* hidden, const void* table, const void* embed
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
+                                   const float* __restrict__ parts, int n_parts, size_t part_stride,
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden_size, float eps,
                                    int write_back) {
@@ -64,12 +68,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
   const int r = rows ? rows[o] : o;
   float* h = hidden + (size_t)r * hidden_size;
   const T* d = delta ? delta + (size_t)r * hidden_size : nullptr;
+  const float* ps = parts ? parts + (size_t)r * hidden_size : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden_size; i += blockDim.x) {
     float v = h[i];
     if (d) v += Elem<T>::load(d + i);
+    if (ps) {
+      float sum = ps[i];
+      for (int sp = 1; sp < n_parts; ++sp) sum += ps[sp * part_stride + i];
+      v += Elem<T>::round(sum);
+    }
     row_cache[i] = v;
-    if (write_back && d) h[i] = v;
+    if (write_back && (d || ps)) h[i] = v;
     ss += v * v;
   }
   const float total = block_sum(ss, scratch);
@@ -109,9 +119,11 @@ template <> struct Pack4<__nv_bfloat16> {
 // few rows of a decode step, and a row's result does not depend on which.
 // REGS: the row fits one pass (hidden_size <= 4 * VT), so a thread keeps its elements in registers between
 // the sum and the scaling instead of parking the row in shared memory; the sums are the same.
-template <typename T, int R, bool REGS>
-__global__ void __launch_bounds__(512, (REGS && R > 1) ? 2 : 4)   // (32 registers where 2,048 threads stay resident)
+// PARTS: the update is the sum of partial sums (see above) instead of `delta`.
+template <typename T, int R, bool REGS, bool PARTS = false>
+__global__ void __launch_bounds__(512, ((REGS && R > 1) || PARTS) ? 2 : 4)   // (32 registers where 2,048 threads stay resident)
 add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
+                                        const float* __restrict__ parts, int n_parts, size_t part_stride,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
                                         int write_back, int settled) {
@@ -121,7 +133,8 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
   const int o = blockIdx.x;
   const int r = rows ? rows[o] : o;            // the step's metadata: not written by the kernel before
   float* h = hidden + (size_t)r * hidden_size;
-  const T* d = delta ? delta + (size_t)r * hidden_size : nullptr;
+  const T* d = (!PARTS && delta) ? delta + (size_t)r * hidden_size : nullptr;
+  const float* ps = PARTS ? parts + (size_t)r * hidden_size : nullptr;
   const int threads = blockDim.x, vt = threads * R;
   // the norm's weight is a constant: this thread's first four are loaded before the wait
   const int i_first = threadIdx.x * 4;
@@ -154,7 +167,20 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
       } else {
         load4(h + i, v);
       }
-      if (d) {
+      if constexpr (PARTS) {
+        float dv[4];
+        load4(ps + i, dv);
+#pragma unroll 4
+        for (int sp = 1; sp < n_parts; ++sp) {
+          float pv[4];
+          load4(ps + sp * part_stride + i, pv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dv[j] += pv[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] += Elem<T>::round(dv[j]);
+        if (write_back) *reinterpret_cast<float4*>(h + i) = make_float4(v[0], v[1], v[2], v[3]);
+      } else if (d) {
         float dv[4];
         Pack4<T>::load(d + i, dv);
 #pragma unroll
@@ -216,9 +242,10 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
   }
 }
 
-ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* weight, void* out,
-                               const int* rows, int n_rows, int hidden_size, float eps, int write_back,
-                               int settled, void* stream) {
+namespace {
+int run_add_rmsnorm(void* hidden, const void* delta, const float* parts, int n_parts, size_t part_stride,
+                    const float* weight, void* out, const int* rows, int n_rows, int hidden_size, float eps,
+                    int write_back, int settled, void* stream) {
   if (n_rows <= 0) return ERB_OK;
   const size_t smem = (size_t)(hidden_size + 32) * sizeof(float);
   if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "add_rmsnorm: hidden_size %d too large", hidden_size);
@@ -232,8 +259,25 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "add_rmsnorm: %s", cudaGetErrorString(e));
   }
   const bool vec = hidden_size % 4 == 0 && !((uintptr_t)hidden & 15) && !((uintptr_t)delta & 7) &&
-                   !((uintptr_t)out & 7) && !((uintptr_t)weight & 15);
-  if (vec) {
+                   !((uintptr_t)out & 7) && !((uintptr_t)weight & 15) && !((uintptr_t)parts & 15) && part_stride % 4 == 0;
+  if (vec && parts) {
+    const bool one_pass = hidden_size <= threads * 4;
+    const size_t small = 32 * sizeof(float);
+    if (one_pass) {
+      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, true, true>, dim3(n_rows), dim3(threads), small, (cudaStream_t)stream,
+          (float*)hidden, (const elem_t*)nullptr, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps,
+          write_back, settled);
+    } else {
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_vec4_kernel<elem_t, 1, false, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "add_rmsnorm: %s", cudaGetErrorString(e));
+      }
+      launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, false, true>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream,
+          (float*)hidden, (const elem_t*)nullptr, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps,
+          write_back, settled);
+    }
+  } else if (vec) {
     // many rows of 2048 and more: half the threads, two virtual threads each (same sums, see the kernel)
     const bool halve = threads == 512 && n_rows > 64;
     const bool one_pass = hidden_size <= threads * 4;     // a row fits the registers of its block
@@ -245,21 +289,38 @@ ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* wei
     const size_t small = 32 * sizeof(float);
     if (halve && one_pass)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2, true>, dim3(n_rows), dim3(256), small, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
+          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
     else if (halve)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 2, false>, dim3(n_rows), dim3(256), smem, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
+          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
     else if (one_pass)
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, true>, dim3(n_rows), dim3(threads), small, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
+          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
     else
       launch_chained(add_rmsnorm_vec4_kernel<elem_t, 1, false>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
-          (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
+          (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
   } else {
     launch_chained(add_rmsnorm_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
-        (const elem_t*)delta, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+        (const elem_t*)delta, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
   }
   return check_launch("add_rmsnorm");
+}
+}  // namespace
+
+ERB_EXPORT int erb_add_rmsnorm(void* hidden, const void* delta, const float* weight, void* out,
+                               const int* rows, int n_rows, int hidden_size, float eps, int write_back,
+                               int settled, void* stream) {
+  return run_add_rmsnorm(hidden, delta, nullptr, 0, 0, weight, out, rows, n_rows, hidden_size, eps, write_back, settled, stream);
+}
+
+// The same with the update given as `n_parts` arrays of partial sums [rows of hidden][hidden_size], float,
+// `part_stride` floats from one to the next; they are added in their order.
+ERB_EXPORT int erb_add_rmsnorm_parts(void* hidden, const float* parts, int n_parts, long long part_stride, const float* weight,
+                                     void* out, const int* rows, int n_rows, int hidden_size, float eps, int write_back,
+                                     int settled, void* stream) {
+  if (!parts || n_parts < 1 || part_stride < 0) return fail(ERB_ERR_ARG, "add_rmsnorm_parts: bad arguments");
+  return run_add_rmsnorm(hidden, nullptr, parts, n_parts, (size_t)part_stride, weight, out, rows, n_rows, hidden_size, eps,
+                         write_back, settled, stream);
 }
 
 // hidden[row] += delta[row] without a norm (the last residual of a stack that ends without one).
@@ -268,6 +329,29 @@ __global__ void residual_add_kernel(float* __restrict__ hidden, const T* __restr
   chain_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) hidden[i] += Elem<T>::load(delta + i);
+}
+
+// hidden += round_T(p0 + p1 + ...) for float partial sums, `part_stride` floats apart.
+template <typename T>
+__global__ void residual_add_parts_kernel(float* __restrict__ hidden, const float* __restrict__ parts, int n_parts,
+                                          size_t part_stride, size_t n) {
+  chain_wait();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float sum = parts[i];
+  for (int sp = 1; sp < n_parts; ++sp) sum += parts[sp * part_stride + i];
+  hidden[i] += Elem<T>::round(sum);
+}
+
+ERB_EXPORT int erb_residual_add_parts(void* hidden, const float* parts, int n_parts, long long part_stride, long long n,
+                                      void* stream) {
+  if (n <= 0) return ERB_OK;
+  if (!parts || n_parts < 1 || part_stride < 0) return fail(ERB_ERR_ARG, "residual_add_parts: bad arguments");
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+  launch_chained(residual_add_parts_kernel<elem_t>, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, (float*)hidden, parts,
+      n_parts, (size_t)part_stride, (size_t)n);
+  return check_launch("residual_add_parts");
 }
 
 ERB_EXPORT int erb_residual_add(void* hidden, const void* delta, long long n, void* stream) {

@@ -61,6 +61,11 @@ const char* status_name(cublasStatus_t s) {
       return fail(ERB_ERR_CUDA, "linear: %s -> %s", #expr, status_name(st__));                 \
   } while (0)
 
+int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return (v && v[0]) ? atoi(v) : fallback;
+}
+
 bool tuning_enabled() {
   static const bool on = [] {
     const char* v = getenv("EDGERAG_B200_NO_TUNE");
@@ -77,6 +82,7 @@ bool tuning_enabled() {
 // the 513 to 576 rows of a serving step picked algorithms that were slower inside the step (weights from
 // DRAM) than the library's first choice, and the odd row counts of such steps would each pay for a trial.
 constexpr int kTuneFromRows = 1024, kTuneAtUse = 3;
+constexpr size_t kFlushBytes = 192u << 20;
 
 int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f32, int accumulate,
               size_t ws_bytes) {
@@ -102,7 +108,7 @@ int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f
   LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws_bytes,
                                                 sizeof(ws_bytes)));
   int found = 0;
-  const int want = (M >= kTuneFromRows && tuning_enabled()) ? 8 : 1;   // more than one only where they get timed
+  const int want = (M >= env_int("EDGERAG_B200_TUNE_FROM_ROWS", kTuneFromRows) && tuning_enabled()) ? 8 : 1;   // more than one only where they get timed
   cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(g_handle, p.op, p.a, p.b, p.c, p.c, pref, want, p.candidates, &found);
   cublasLtMatmulPreferenceDestroy(pref);
   if (st != CUBLAS_STATUS_SUCCESS || found == 0)
@@ -114,15 +120,21 @@ int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f
   return ERB_OK;
 }
 
-void tune_plan(Plan& p, int M, const void* a, const void* w, void* out, void* workspace, size_t ws, cudaStream_t stream) {
-  if (p.n_candidates < 2 || M < kTuneFromRows || !tuning_enabled()) { p.tuned = true; return; }
+void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void* out, void* workspace, size_t ws, cudaStream_t stream) {
+  static const int from_rows = env_int("EDGERAG_B200_TUNE_FROM_ROWS", kTuneFromRows);
+  static const bool log = env_int("EDGERAG_B200_TUNE_LOG", 0) != 0;
+  if (p.n_candidates < 2 || M < from_rows || !tuning_enabled()) { p.tuned = true; return; }
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) return;
   if (++p.uses < kTuneAtUse) return;
   p.tuned = true;
+  // In a step the weights of a product come from DRAM (a layer's weights pass through L2 long before
+  // the layer runs again), so every timed run starts after a buffer larger than L2 has been written.
+  void* flush = nullptr;
+  if (cudaMalloc(&flush, kFlushBytes) != cudaSuccess) { cudaGetLastError(); return; }
   cudaEvent_t t0, t1;
-  if (cudaEventCreate(&t0) != cudaSuccess) return;
-  if (cudaEventCreate(&t1) != cudaSuccess) { cudaEventDestroy(t0); return; }
+  if (cudaEventCreate(&t0) != cudaSuccess) { cudaFree(flush); return; }
+  if (cudaEventCreate(&t1) != cudaSuccess) { cudaEventDestroy(t0); cudaFree(flush); return; }
   const float alpha = 1.f, beta = 0.f;
   float best = 1e30f;
   int best_i = 0;
@@ -130,18 +142,25 @@ void tune_plan(Plan& p, int M, const void* a, const void* w, void* out, void* wo
     const cublasLtMatmulHeuristicResult_t& c = p.candidates[i];
     if (c.state != CUBLAS_STATUS_SUCCESS || c.workspaceSize > ws) continue;
     bool ok = true;
+    float total = 0.f;
     for (int r = 0; r < 4 && ok; ++r) {     // one to warm up, three timed
-      if (r == 1) cudaEventRecord(t0, stream);
+      cudaMemsetAsync(flush, r, kFlushBytes, stream);
+      cudaEventRecord(t0, stream);
       ok = cublasLtMatmul(g_handle, p.op, &alpha, w, p.a, a, p.b, &beta, out, p.c, out, p.c, &c.algo, workspace, ws,
                           stream) == CUBLAS_STATUS_SUCCESS;
+      cudaEventRecord(t1, stream);
+      float ms = 0.f;
+      ok = ok && cudaEventSynchronize(t1) == cudaSuccess && cudaEventElapsedTime(&ms, t0, t1) == cudaSuccess;
+      if (r) total += ms;
     }
-    cudaEventRecord(t1, stream);
-    if (cudaEventSynchronize(t1) != cudaSuccess || !ok) continue;
-    float ms = 0.f;
-    if (cudaEventElapsedTime(&ms, t0, t1) == cudaSuccess && ms < best) { best = ms; best_i = i; }
+    if (!ok) { cudaGetLastError(); continue; }
+    if (log) fprintf(stderr, "[edgerag_b200] linear %d x %d x %d: proposal %d, %.1f us\n", M, N, K,
+                     i, total / 3 * 1000);
+    if (total < best) { best = total; best_i = i; }
   }
   cudaEventDestroy(t0);
   cudaEventDestroy(t1);
+  cudaFree(flush);
   p.algo = p.candidates[best_i].algo;
   p.workspace = p.candidates[best_i].workspaceSize;
 }
@@ -167,7 +186,7 @@ ERB_EXPORT int erb_linear(const void* a, const void* w, void* out, int M, int N,
     it = g_plans.emplace(key, p).first;
   }
   Plan& p = it->second;
-  if (!p.tuned && !accumulate) tune_plan(p, M, a, w, out, workspace, ws, (cudaStream_t)stream);
+  if (!p.tuned && !accumulate) tune_plan(p, M, N, K, a, w, out, workspace, ws, (cudaStream_t)stream);
   const float alpha = 1.f, beta = accumulate ? 1.f : 0.f;
   LT_CHECK(cublasLtMatmul(g_handle, p.op, &alpha, w, p.a, a, p.b, &beta, out, p.c, out, p.c, &p.algo,
                           workspace, ws, (cudaStream_t)stream));

@@ -19,6 +19,12 @@
 // through distributed shared memory.  The split is a function of N and K alone, and a row of `a` is a column of the
 // accumulator that no other row touches: an output's bits do not depend on how many rows a has.
 //
+// Or the k of a tile is split over independent blocks (no cluster) that each leave their float sums as one
+// of `splits` partial results [M, N], for a consumer that adds them in order while it reads (the residual
+// add + norm after the attention output and the down projection).  A block of such a launch takes only
+// the stages its slice of k needs, so that two fit an SM or one fits beside the kernel before it, and all
+// its first tiles of w are on their way before that kernel has finished.
+//
 // Every wait is bounded; a thread that gives up raises a block-wide flag, the block lets its copies land,
 // records 4000000 + block in *status (if given), frees its TMEM and writes nothing.
 #include <stdarg.h>
@@ -47,7 +53,8 @@ constexpr uint32_t kTmemCols = 64;
 constexpr int kMaxCluster = 8;
 
 struct Epilogue {
-  int mode;                    // 0: bfloat16 out, 1: float out, 2: gated (w rows: 64 gate + 64 up per tile), 3: rotary + cache write
+  int mode;                    // 0: bfloat16 out, 1: float out, 2: gated (w rows: 64 gate + 64 up per tile), 3: rotary + cache write,
+                               // 4: float partial results [splits][M][ldo], one per slice of k (no cluster)
   // mode 3
   const int* positions;        // per row of a
   const float* inv_freq;       // [head_dim / 2]
@@ -84,16 +91,38 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const bool gated = ep.mode == 2;
   // rows of w of this tile: 128 neighbours, or for the gated product 64 gate rows and the 64 up rows that go with them
   const int n0 = tile * (gated ? kTileN / 2 : kTileN);
+  const bool parts = ep.mode == 4;
+  const bool clustered = splits > 1 && !parts;
   const int k_blocks = (K + kTileK - 1) / kTileK;
   const int per_rank = (k_blocks + splits - 1) / splits;
-  const int kb0 = rank * per_rank, kb1 = min(k_blocks, kb0 + per_rank);
+  // partial results: slices as even as they get; a cluster: whole shares, the last one short
+  const int kb0 = parts ? (int)((long long)rank * k_blocks / splits) : rank * per_rank;
+  const int kb1 = parts ? (int)((long long)(rank + 1) * k_blocks / splits) : min(k_blocks, kb0 + per_rank);
   const int n_kb = max(0, kb1 - kb0);
 
+  constexpr uint32_t kABytes = MT * kTileK * 2;
+  // The tiles of w are constants: the copy thread asks for the first stages as soon as it has set up the
+  // barriers, before the block's other preparations and before the kernel before this one has finished.
+  auto ask_w = [&](int i) {
+    const int s = i % kStages;
+    mbar_expect(full0 + 8 * s, kWBytes + kABytes);
+    const uint32_t dst = base + s * kStageBytes;
+    if (gated) {
+      tma_load_2d(dst, &map_w, (kb0 + i) * kTileK, n0, full0 + 8 * s);
+      tma_load_2d(dst + kWBytes / 2, &map_w, (kb0 + i) * kTileK, N + n0, full0 + 8 * s);
+    } else {
+      tma_load_2d(dst, &map_w, (kb0 + i) * kTileK, n0, full0 + 8 * s);
+    }
+  };
+  const int ahead = min(kStages, n_kb);
   if (tid == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     mbar_init(done_bar, 1);
     s_abort = 0;
     mbar_init_fence();
+    for (int i = 0; i < ahead; ++i) ask_w(i);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
@@ -104,30 +133,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   fence_after_sync();
   const uint32_t tmem = tmem_slot;
   volatile int* abort_flag = &s_abort;
-  constexpr uint32_t kABytes = MT * kTileK * 2;
-  int asked = 0;                        // stages the copy thread has asked for
+  int asked = tid == 0 ? ahead : 0;     // stages the copy thread has asked for
 
   if (warp == 0) {
     if (lane == 0) {
-      // The tiles of w are constants: the first stages are asked for before the kernel before this one
-      // has finished; the tiles of a (its output) only after.
-      auto ask_w = [&](int i) {
-        const int s = i % kStages;
-        mbar_expect(full0 + 8 * s, kWBytes + kABytes);
-        const uint32_t dst = base + s * kStageBytes;
-        if (gated) {
-          tma_load_2d(dst, &map_w, (kb0 + i) * kTileK, n0, full0 + 8 * s);
-          tma_load_2d(dst + kWBytes / 2, &map_w, (kb0 + i) * kTileK, N + n0, full0 + 8 * s);
-        } else {
-          tma_load_2d(dst, &map_w, (kb0 + i) * kTileK, n0, full0 + 8 * s);
-        }
-      };
+      // the tiles of a (the output of the kernel before this one) only after the wait
       auto ask_a = [&](int i) {
         const int s = i % kStages;
         tma_load_2d(base + s * kStageBytes + kWBytes, &map_a, (kb0 + i) * kTileK, 0, full0 + 8 * s);
       };
-      const int ahead = min(kStages, n_kb);
-      for (int i = 0; i < ahead; ++i) ask_w(i);
       chain_wait();
       for (int i = 0; i < ahead; ++i) ask_a(i);
       asked = ahead;
@@ -171,7 +185,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (status) atomicCAS(status, 0, 4000000 + (int)blockIdx.x);
     }
     __syncthreads();
-    if (splits > 1) { cluster_sync_all(); cluster_sync_all(); }
+    if (clustered) { cluster_sync_all(); cluster_sync_all(); }
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     return;
   }
@@ -204,9 +218,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   // With the k of a tile split over a cluster, every block finishes the rows m of a with m % splits == its
   // rank: it adds what all blocks hold for those rows, in rank order (its own part in its place), reading
   // the others' through distributed shared memory, 16 bytes at a time and all parts of a value at once.
-  const int m_first = splits > 1 ? rank : 0, m_step = splits > 1 ? splits : 1;
+  const int m_first = clustered ? rank : 0, m_step = clustered ? splits : 1;
   const int m_count = M > m_first ? (M - m_first + m_step - 1) / m_step : 0;
-  if (splits > 1) {
+  if (clustered) {
     cluster_sync_all();
     uint32_t remote[kMaxCluster];
 #pragma unroll
@@ -235,7 +249,21 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   }
 
   // ---- finishing ----
-  if (ep.mode <= 1) {
+  if (parts) {
+    // 16 bytes a thread, a row of a after the other (scattered 4-byte stores straight from the accumulator's
+    // registers were slower: 10.6 against 9.6 us for the down projection at 64 rows)
+    float* dst = reinterpret_cast<float*>(out) + (size_t)rank * M * ldo;
+    for (int idx = tid; idx < M * (kTileN / 4); idx += kThreads) {
+      const int m = idx / (kTileN / 4), c4 = (idx % (kTileN / 4)) * 4, n = n0 + c4;
+      const float4 v = *reinterpret_cast<const float4*>(sums + m * kTileN + c4);
+      if (n + 3 < N) {
+        *reinterpret_cast<float4*>(dst + (size_t)m * ldo + n) = v;
+      } else {
+        const float e[4] = {v.x, v.y, v.z, v.w};
+        for (int j = 0; j < 4 && n + j < N; ++j) dst[(size_t)m * ldo + n + j] = e[j];
+      }
+    }
+  } else if (ep.mode <= 1) {
     for (int idx = tid; idx < m_count * kTileN; idx += kThreads) {
       const int m = m_first + (idx / kTileN) * m_step, n = n0 + idx % kTileN;
       if (n >= N) continue;
@@ -319,6 +347,17 @@ int k_splits(int n_tiles, int K) {
   return s < 1 ? 1 : s;
 }
 
+// Independent blocks per tile of w rows for partial results: as many as make about one block per SM, each
+// with at least two stages of 64 k, at most kMaxParts.  A function of N and K only.
+constexpr int kMaxParts = 16;
+int k_parts(int n_tiles, int K) {
+  const int k_blocks = (K + kTileK - 1) / kTileK;
+  int s = sm_count() / n_tiles;
+  if (s > kMaxParts) s = kMaxParts;
+  while (s > 1 && k_blocks / s < 2) --s;
+  return s < 1 ? 1 : s;
+}
+
 template <int MT>
 int launch(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K, int ldo, int n_tiles, int splits,
            const Epilogue& ep, cudaStream_t stream) {
@@ -333,10 +372,17 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N
   cfg.gridDim = dim3(n_tiles, splits);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
+  if (ep.mode == 4) {
+    // the stages that the longest slice of k touches, and room for the sums [MT][128] afterwards
+    const int k_blocks = (K + kTileK - 1) / kTileK, longest = (k_blocks + splits - 1) / splits;
+    const uint32_t stages = (uint32_t)(longest < kStages ? longest : kStages);
+    const uint32_t need = stages * kStageBytes, sums = (uint32_t)MT * kTileN * 4;
+    cfg.dynamicSmemBytes = (need > sums ? need : sums) + 1024;
+  }
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int n = 0;
-  if (splits > 1) {
+  if (splits > 1 && ep.mode != 4) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
     attr[n].val.clusterDim.x = 1;
     attr[n].val.clusterDim.y = splits;
@@ -367,7 +413,7 @@ int run(const void* a, const void* w, void* out, int M, int N, int K, int lda, i
   if ((rc = matrix_map(&mw, w, w_rows, K, ldw, ep.mode == 2 ? kTileN / 2 : kTileN)) || (rc = matrix_map(&ma, a, M, K, lda, MT))) return rc;
   const int per_tile = ep.mode == 2 ? kTileN / 2 : kTileN;
   const int n_tiles = ((ep.mode == 3 ? w_rows : N) + per_tile - 1) / per_tile;
-  const int splits = k_splits(n_tiles, K);
+  const int splits = ep.mode == 4 ? k_parts(n_tiles, K) : k_splits(n_tiles, K);
   switch (MT) {
     case 16: return launch<16>(mw, ma, out, M, N, K, ldo, n_tiles, splits, ep, stream);
     case 32: return launch<32>(mw, ma, out, M, N, K, ldo, n_tiles, splits, ep, stream);
@@ -392,6 +438,19 @@ ERB_EXPORT int erb_linear_tc(const void* a, const void* w, void* out, int M, int
   Epilogue ep = {};
   ep.mode = out_f32 ? 1 : 0;
   return run(a, w, out, M, N, K, lda, ldw, ldo, N, ep, (cudaStream_t)stream);
+}
+
+// The number of partial results that erb_linear_tc_parts leaves for a product with N rows of w and K columns.
+ERB_EXPORT int erb_linear_tc_parts_count(int N, int K) { return k_parts((N + kTileN - 1) / kTileN, K); }
+
+// parts[s][M][ldo] (float), s < erb_linear_tc_parts_count(N, K): the sums over the s-th slice of k of
+// a[M, K] * w[N, K]^T; the product is their sum.  1 <= M <= 64.
+ERB_EXPORT int erb_linear_tc_parts(const void* a, const void* w, void* parts, int M, int N, int K, int lda, int ldw, int ldo,
+                                   void* stream) {
+  if (ldo < N || (ldo & 3) || ((uintptr_t)parts & 15)) return fail(ERB_ERR_ARG, "linear_tc_parts: bad sizes");
+  Epilogue ep = {};
+  ep.mode = 4;
+  return run(a, w, parts, M, N, K, lda, ldw, ldo, N, ep, (cudaStream_t)stream);
 }
 
 // Gated product: w holds N gate rows and then N up rows ([2N, K]); out[M, N] = silu(g) * u with

@@ -125,7 +125,7 @@ class DecoderModel:
                                     settled=kernels.launches() > ctx.stream_written)
         else:
             if delta is not None:
-                kernels.residual_add(hidden, delta)
+                kernels.residual_add(hidden, delta, self.dtype)
             kernels.gather_cast(hidden, y, ctx.want_rows)
         logits = ctx.buf("model.logits", (w, self.logits_stride), torch.float32)[:, : self.vocab_size]
         self.head.forward(y, logits)

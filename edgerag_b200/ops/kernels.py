@@ -40,6 +40,11 @@ _SIGNATURES = {
     "erb_linear_skinny_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "erb_linear_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_linear_tc_parts": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_linear_tc_parts_count": [c_int, c_int],
+    "erb_residual_add_parts": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
+    "erb_add_rmsnorm_parts": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                              c_int, c_int, c_void_p],
     "erb_linear_tc_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_tc_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -149,24 +154,43 @@ def add_rmsnorm(hidden: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, e
                 delta: torch.Tensor | None = None, rows: torch.Tensor | None = None,
                 write_back: bool = True, settled: bool = False) -> None:
     """out = weight * round(rmsnorm(hidden (+ delta))); hidden += delta in place when write_back.
+    ``delta``: rows of the element type, or float32 partial sums ``[parts, rows, width]`` (what
+    ``linear_parts`` leaves) that are added in their order and rounded to the element type once, so that
+    the update is what a product stored in the element type would have been.
     ``settled``: ``hidden`` was last written two or more launches ago (the launch just before this one
     wrote ``delta`` at most), so the kernel may read it while that launch is still running."""
     _need(hidden, "hidden", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
-    _need(delta, "delta", out.dtype); _need(rows, "rows", torch.int32)
+    _need(rows, "rows", torch.int32)
     h = hidden.shape[1]
     n = out.shape[0]
-    if out.shape[1] != h or weight.numel() != h or (delta is not None and delta.shape != hidden.shape):
+    in_parts = delta is not None and delta.dim() == 3
+    _need(delta, "delta", torch.float32 if in_parts else out.dtype)
+    if out.shape[1] != h or weight.numel() != h or (delta is not None and delta.shape[-2:] != hidden.shape):
         raise KernelError("add_rmsnorm: shapes disagree")
     if rows is None and n != hidden.shape[0]:
         raise KernelError("add_rmsnorm: out rows differ from hidden rows")
     if rows is not None and rows.numel() < n:
         raise KernelError("add_rmsnorm: fewer row indices than output rows")
+    if in_parts:
+        _call(_fn("elementwise", _elem(out), "erb_add_rmsnorm_parts"), hidden.data_ptr(), delta.data_ptr(), delta.shape[0],
+              delta.stride(0), weight.data_ptr(), out.data_ptr(), _ptr(rows), n, h, float(eps),
+              int(write_back and rows is None), int(bool(settled)), _stream())
+        return
     _call(_fn("elementwise", _elem(out), "erb_add_rmsnorm"), hidden.data_ptr(), _ptr(delta), weight.data_ptr(),
           out.data_ptr(), _ptr(rows), n, h, float(eps), int(write_back and rows is None), int(bool(settled)), _stream())
 
 
-def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
+def residual_add(hidden: torch.Tensor, delta: torch.Tensor, dtype: torch.dtype | None = None) -> None:
+    """hidden += delta: rows of the model's element type, or float32 partial sums ``[parts, rows, width]``,
+    which are added up and rounded to ``dtype`` (the model's element type) once, as ``add_rmsnorm`` does."""
     _need(hidden, "hidden", torch.float32); _need(delta, "delta")
+    if delta.dim() == 3:
+        _need(delta, "delta", torch.float32)
+        if delta.shape[1:] != hidden.shape or dtype is None:
+            raise KernelError("residual_add: partial sums need [parts, rows, width] and the element type to round to")
+        _call(_fn("elementwise", _ELEM[dtype], "erb_residual_add_parts"), hidden.data_ptr(), delta.data_ptr(), delta.shape[0],
+              delta.stride(0), hidden.numel(), _stream())
+        return
     if hidden.shape != delta.shape:
         raise KernelError("residual_add: shapes disagree")
     _call(_fn("elementwise", _elem(delta), "erb_residual_add"), hidden.data_ptr(), delta.data_ptr(),
@@ -306,6 +330,39 @@ def linear_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("linear_tc: operands not supported")
     _call(_fn_tc("erb_linear_tc"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, lda, k, ldo,
           int(out.dtype == torch.float32), _stream())
+
+
+def linear_parts_count(a: torch.Tensor, weight: torch.Tensor) -> int:
+    """How many partial results ``linear_parts`` leaves for ``a @ weight^T``, or 0 where the product is
+    not taken in parts: it is for the bfloat16 rows of a decode step beyond the register kernel's
+    (``SKINNY_MAX_ROWS`` < rows <= ``TC_MAX_ROWS``) against a weight with so few rows that whole tiles of
+    them would leave most SMs without work (the attention output and the down projection)."""
+    m, k = a.shape
+    n = weight.shape[0]
+    if not (SKINNY_MAX_ROWS < m <= TC_MAX_ROWS) or a.dtype != torch.bfloat16 or n % 4 or a.stride(1) != 1:
+        return 0
+    if not linear_few_rows_supported(a, weight, a.stride(0)) or -(-n // 128) * 2 > _sms(a.device):
+        return 0
+    return _parts_count(n, k)
+
+
+@functools.lru_cache(maxsize=256)
+def _parts_count(n: int, k: int) -> int:
+    return int(_fn_tc("erb_linear_tc_parts_count")(n, k))
+
+
+def linear_parts(a: torch.Tensor, weight: torch.Tensor, parts: torch.Tensor) -> None:
+    """``parts[s] = a[:, slice s of k] @ weight[:, slice s of k]^T`` in float32 for the
+    ``linear_parts_count`` slices of k; their sum in order is the product (``add_rmsnorm`` and
+    ``residual_add`` take them as they are)."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
+    _need(parts, "parts", torch.float32)
+    m, k = a.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or a.stride(1) != 1 or tuple(parts.shape) != (linear_parts_count(a, weight), m, n):
+        raise KernelError("linear_parts: shapes disagree or the product is not taken in parts")
+    _call(_fn_tc("erb_linear_tc_parts"), a.data_ptr(), weight.data_ptr(), parts.data_ptr(), m, n, k, a.stride(0), k, n,
+          _stream())
 
 
 def linear_tc_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:

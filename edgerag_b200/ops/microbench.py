@@ -159,11 +159,17 @@ def linear(a) -> dict:
     x = torch.randn((a.m, a.k), device="cuda").to(dtype)
     out = torch.empty((a.m, a.n), device="cuda", dtype=torch.float32 if a.out32 else dtype)
     out_glu = torch.empty((a.m, a.n // 2), device="cuda", dtype=dtype) if a.glu else None
+    n_parts = kernels.linear_parts_count(x, ws[0]) if a.parts else 0
+    if a.parts and not n_parts:
+        raise SystemExit("this product is not taken in parts (17 to 64 bfloat16 rows, a weight of few rows)")
+    parts = torch.empty((n_parts, a.m, a.n), device="cuda", dtype=torch.float32) if n_parts else None
     state = {"i": 0}
 
     def fn():
         state["i"] = (state["i"] + 1) % reps
-        if a.tc:
+        if a.parts:
+            kernels.linear_parts(x, ws[state["i"]], parts)
+        elif a.tc:
             (kernels.linear_tc_glu if a.glu else kernels.linear_tc)(x, ws[state["i"]], out_glu if a.glu else out)
         elif a.glu:
             kernels.linear_glu(x, ws[state["i"]], out_glu)
@@ -173,7 +179,9 @@ def linear(a) -> dict:
     us = _time(fn, a.iters, a.warmup)
     nbytes = a.n * a.k * x.element_size() + a.m * a.k * x.element_size() + out.numel() * out.element_size()
     flops = 2.0 * a.m * a.n * a.k
-    return {"case": "linear", "m": a.m, "n": a.n, "k": a.k, "library": bool(a.library), "tc": bool(a.tc), "glu": bool(a.glu), "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+    if n_parts:
+        nbytes += parts.numel() * 4 - out.numel() * out.element_size()
+    return {"case": "linear", "m": a.m, "n": a.n, "k": a.k, "library": bool(a.library), "tc": bool(a.tc), "glu": bool(a.glu), "parts": n_parts, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
             "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4), "tflops": round(flops / us / 1e6, 2)}
 
 
@@ -321,6 +329,7 @@ def main(argv=None) -> int:
     g.add_argument("--out32", action="store_true")
     g.add_argument("--library", action="store_true", help="force the library product (cuBLASLt) also for few rows")
     g.add_argument("--tc", action="store_true", help="the TMA + tcgen05 weight-streaming kernel (up to 64 rows)")
+    g.add_argument("--parts", action="store_true", help="the slices of k as float32 partial results (17 to 64 rows, a weight of few rows)")
     g.add_argument("--glu", action="store_true", help="the gated product: w is [gate; up] of n rows, out has n / 2 columns")
     k = sub.add_parser("step-kernels", parents=[common])
     k.add_argument("--layers", type=int, default=4)

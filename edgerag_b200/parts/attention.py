@@ -114,6 +114,11 @@ class Attention(Mixer):
         elif n > nd:
             kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:],
                                    out[nd:], self.n_q, self.scale, window=self.window)
+        n_parts = kernels.linear_parts_count(out, self.w_o)
+        if n_parts:      # the rows of a larger decode step: k split over the SMs, the norm after adds the parts
+            y = ctx.buf("mixer.out_parts", (n_parts, n, self.hidden), torch.float32)
+            kernels.linear_parts(out, self.w_o, y)
+            return y
         y = ctx.buf("mixer.out", (n, self.hidden), self.dtype)
         kernels.linear(out, self.w_o, y)
         return y

@@ -117,7 +117,8 @@ class Norm(Part):
     def forward(self, hidden: torch.Tensor, out: torch.Tensor, delta: torch.Tensor | None = None,
                 rows: torch.Tensor | None = None, write_back: bool = True, settled: bool = False) -> None:
         """``hidden`` (float32, the residual stream) gets ``delta`` added in place when given and
-        ``write_back``; ``out`` receives the normed rows (all rows, or ``rows`` of them).  ``settled`` is a
+        ``write_back``; ``out`` receives the normed rows (all rows, or ``rows`` of them).  ``delta`` is
+        ``[rows, hidden]`` of the model's element type or float32 partial sums ``[parts, rows, hidden]``.  ``settled`` is a
         hint that a norm may ignore: the caller vouches that ``hidden`` was not written by the kernel
         launched just before this call (only ``delta`` was), so it may be read while that kernel runs."""
         raise NotImplementedError
@@ -148,11 +149,15 @@ class Mixer(Part):
         return None
 
     def forward(self, x: torch.Tensor, ctx: Any, call: LayerCall) -> torch.Tensor:
+        """The update of the residual stream for the normed rows ``x``: ``[rows, hidden]`` of the model's
+        element type, or float32 partial sums ``[parts, rows, hidden]`` whose sum in order is the update
+        (a norm adds them as it reads)."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
+        """As ``Mixer.forward``: the update, whole or as float32 partial sums."""
         raise NotImplementedError
 
 

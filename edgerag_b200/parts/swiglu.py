@@ -41,6 +41,11 @@ class SwiGLU(FeedForward):
             gate_up = ctx.buf("ffn.gate_up", (n, 2 * self.intermediate), self.dtype)
             kernels.linear(x, self.w_gate_up, gate_up)
             kernels.swiglu(gate_up, act)
+        n_parts = kernels.linear_parts_count(act, self.w_down)
+        if n_parts:      # the rows of a larger decode step: k split over the SMs, the norm after adds the parts
+            y = ctx.buf("ffn.out_parts", (n_parts, n, self.hidden), torch.float32)
+            kernels.linear_parts(act, self.w_down, y)
+            return y
         y = ctx.buf("ffn.out", (n, self.hidden), self.dtype)
         kernels.linear(act, self.w_down, y)
         return y

@@ -159,6 +159,17 @@ def cuttings_agree(trace: Trace, results: dict[int, np.ndarray], rids: list[str]
     return {"max_fraction": worst / scale, "mean_fraction": mean / scale, "scale": scale}
 
 
+def whole_update(y: torch.Tensor) -> torch.Tensor:
+    """The update that a mixer or feed-forward returned, as float32 rows: itself, or for float32 partial sums
+    ``[parts, rows, width]`` (the rows of a larger decode step) their sum in order, as the next norm adds them."""
+    if y.dim() == 2:
+        return y.float()
+    total = y[0].clone()
+    for part in y[1:]:
+        total += part
+    return total
+
+
 def random_sequence(vocab: int, n: int, seed: int) -> list[int]:
     gen = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=gen).tolist()

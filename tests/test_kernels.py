@@ -95,6 +95,45 @@ def test_add_rmsnorm_gives_a_row_the_same_bits_in_any_batch(k, dtype, width):
     assert torch.equal(out_few, out_many[120:125]) and torch.equal(few, h[120:125])
 
 
+def test_product_in_parts_and_the_norm_that_adds_them(k):
+    """17 to 64 bfloat16 rows against a weight of few rows: the slices of k as float32 partial results
+    (against float64, N and K no multiples of a tile), a row's parts the same bits whatever the number
+    of rows, and the residual add + norm that takes the parts against the same norm fed their sum."""
+    for m, n, kk in ((17, 2048, 2048), (64, 2048, 8192), (40, 960, 2560), (33, 204, 1032), (64, 576, 1536), (24, 100, 136)):
+        a, w = rand((m, kk), torch.bfloat16, 180 + m, 0.5), rand((n, kk), torch.bfloat16, 181 + m, 0.5)
+        count = k.linear_parts_count(a, w)
+        assert count >= 1 and k.linear_parts_count(a[:16], w) == 0
+        parts = torch.full((count, m, n), float("nan"), dtype=torch.float32, device="cuda")
+        k.linear_parts(a, w, parts)
+        total = parts[0].clone()
+        for s in range(1, count):
+            total += parts[s]
+        torch.testing.assert_close(total.double(), a.double() @ w.double().T, atol=2e-3 * (kk ** 0.5) / 8, rtol=1e-4)
+        if count > 1:       # the slices cover k once: each differs from the whole
+            assert float((parts[0].double() - total.double()).abs().max()) > 1e-3
+        fewer = torch.empty((count, 17, n), dtype=torch.float32, device="cuda")
+        k.linear_parts(a[:17], w, fewer)
+        assert torch.equal(fewer, parts[:, :17])
+        # the norm: hidden += sum of the parts, in their order
+        weight = rand((n,), torch.float32, 7).add_(1.0)
+        hidden = rand((m, n), torch.float32, 8, 2.0)
+        h_parts, h_sum = hidden.clone(), hidden.clone()
+        out_parts = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        k.add_rmsnorm(h_parts, weight, out_parts, 1e-5, delta=parts)
+        summed = hidden + total.bfloat16().float()      # the parts' sum is rounded once, like a stored product
+        assert torch.equal(h_parts, summed)
+        x = summed * torch.rsqrt(summed.pow(2).mean(-1, keepdim=True) + 1e-5)
+        torch.testing.assert_close(out_parts.float(), (weight * x.bfloat16().float()).bfloat16().float(), **tol(torch.bfloat16))
+        rows = torch.tensor([m - 1, 0, 5], dtype=torch.int32).cuda()
+        picked = torch.empty((3, n), dtype=torch.bfloat16, device="cuda")
+        k.add_rmsnorm(h_sum, weight, picked, 1e-5, delta=parts, rows=rows, write_back=False)
+        assert torch.equal(h_sum, hidden) and torch.equal(picked, out_parts[rows.long()])
+        k.residual_add(h_sum, parts, torch.bfloat16)
+        assert torch.equal(h_sum, summed)
+    # weights with many rows are not taken in parts (whole tiles of them fill the SMs)
+    assert k.linear_parts_count(rand((40, 256), torch.bfloat16, 1), rand((49155, 256), torch.bfloat16, 2)) == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rot", [48, 32])
 def test_rope_cache_write(k, dtype, rot):

@@ -7,6 +7,7 @@ from __future__ import annotations
 import pytest
 import torch
 
+import helpers
 import plain_llama as plain
 
 pytestmark = pytest.mark.gpu
@@ -96,13 +97,13 @@ def test_attention_mixer_whole_and_continued(rig):
     got = []
     for lo, hi in ((0, n1), (n1, n1 + n2)):
         ctx, ordered = runner.prepare([StepEntry("m", tokens=[1] * (hi - lo))])
-        got.append(mixer.forward(x_all[lo:hi].cuda().contiguous(), ctx, call).float().cpu())
+        got.append(helpers.whole_update(mixer.forward(x_all[lo:hi].cuda().contiguous(), ctx, call)).cpu())
         runner.finish(ordered)
     assert_close_scaled(torch.cat(got), want, dtype)
     # one more token: the decode kernel's path
     ctx, ordered = runner.prepare([StepEntry("m", tokens=[1])])
     x_new = (0.5 * torch.randn((1, cfg["hidden"]), generator=torch.Generator().manual_seed(3))).to(engine.dtype)
-    y = mixer.forward(x_new.cuda(), ctx, call).float().cpu()
+    y = helpers.whole_update(mixer.forward(x_new.cuda(), ctx, call)).cpu()
     runner.finish(ordered)
     full = plain.attention(torch.cat([x_all, x_new]).float(), torch.arange(n1 + n2 + 1), w[p + "q_proj.weight"],
                            w[p + "k_proj.weight"], w[p + "v_proj.weight"], w[p + "o_proj.weight"], cfg)
@@ -117,7 +118,7 @@ def test_feed_forward(rig):
     x = torch.randn((7, cfg["hidden"]), generator=torch.Generator().manual_seed(4)).to(engine.dtype)
     p = "model.layers.0.mlp."
     want = plain.swiglu(x.float(), w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
-    got = ffn.forward(x.cuda(), ctx).float().cpu()
+    got = helpers.whole_update(ffn.forward(x.cuda(), ctx)).cpu()
     assert_close_scaled(got, want, dtype)
     engine.runner.finish(ordered)
 
@@ -131,7 +132,7 @@ def test_block_arrangement(rig):
     hidden = h0.clone().cuda()
     delta = block.forward(hidden, None, ctx, engine.model.schedule[0])
     want = plain.decoder_layer(h0, torch.arange(23), w, 0, cfg)
-    assert_close_scaled((hidden + delta.float()).cpu(), want, dtype)
+    assert_close_scaled((hidden + helpers.whole_update(delta)).cpu(), want, dtype)
     engine.runner.finish(ordered)
     engine.runner.release("blk")
 

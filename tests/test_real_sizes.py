@@ -233,8 +233,9 @@ def test_a_request_decodes_to_the_same_bits_whatever_shares_its_step(which, tmp_
     on the number of rows, the norms and the rotary epilogue work row by row, and with ``batch_invariant``
     the attention kernel cuts every sequence into the same splits and groups of heads whatever the batch
     (the twins' context spans two splits).  Beside 31 and 63 others the
-    layers' products are the library's (whose sums depend on the number of rows): there the logits agree
-    within the band of two cuttings of a request."""
+    layers' products are the library's (whose sums depend on the number of rows) and, for the attention
+    output and the down projection, this package's partial sums over slices of k that the next norm adds:
+    there the logits agree within the band of two cuttings of a request."""
     import shutil
 
     from edgerag_b200 import Engine
@@ -260,6 +261,9 @@ def test_a_request_decodes_to_the_same_bits_whatever_shares_its_step(which, tmp_
             rows[beside] = runner.step(entries)[0].clone()
         torch.cuda.synchronize()
         assert torch.isfinite(rows[0]).all()
+        from edgerag_b200.ops import kernels
+        act = torch.empty((32, cfg["inter"]), dtype=torch.bfloat16, device="cuda")
+        assert kernels.linear_parts_count(act, engine.model.blocks[0].ffn.w_down) >= 2      # 32 and 64 rows took that path
         for beside in (7, 15):
             differ = int((rows[beside] != rows[0]).sum())
             assert differ == 0, f"beside {beside} others: {differ} of {rows[0].numel()} logits differ"
