@@ -77,10 +77,10 @@ bool tuning_enabled() {
 // The library's first choice is not always its fastest algorithm for a shape (the products of a 2,048-token
 // portion: 5 % of the step).  A shape with 1,024 rows or more that keeps coming back is worth a look: on its
 // third use outside a stream capture every proposal runs a few times on the caller's operands (each
-// writes the same product to `out`), timed with events, and the fastest stays.  One choice per shape and
-// process.  Not below 1,024 rows: the proposals are timed back to back, with the weights in L2, which for
-// the 513 to 576 rows of a serving step picked algorithms that were slower inside the step (weights from
-// DRAM) than the library's first choice, and the odd row counts of such steps would each pay for a trial.
+// writes the same product to `out`), every run after a write of more than L2's size so that the weights come
+// from DRAM as they do in a step, timed with events, and the fastest stays.  One choice per shape and
+// process.  Not below 1,024 rows: every odd row count of a serving step (513 to 576 rows) would pay for a
+// trial of its own, and for the 17 to 64 rows of a decode step none of the proposals beat the first.
 constexpr int kTuneFromRows = 1024, kTuneAtUse = 3;
 constexpr size_t kFlushBytes = 192u << 20;
 
@@ -142,8 +142,8 @@ void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void*
     const cublasLtMatmulHeuristicResult_t& c = p.candidates[i];
     if (c.state != CUBLAS_STATUS_SUCCESS || c.workspaceSize > ws) continue;
     bool ok = true;
-    float total = 0.f;
-    for (int r = 0; r < 4 && ok; ++r) {     // one to warm up, three timed
+    float fastest = 1e30f;
+    for (int r = 0; r < 6 && ok; ++r) {     // one to warm up, five timed: the fastest counts (what disturbs a run only adds)
       cudaMemsetAsync(flush, r, kFlushBytes, stream);
       cudaEventRecord(t0, stream);
       ok = cublasLtMatmul(g_handle, p.op, &alpha, w, p.a, a, p.b, &beta, out, p.c, out, p.c, &c.algo, workspace, ws,
@@ -151,12 +151,11 @@ void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void*
       cudaEventRecord(t1, stream);
       float ms = 0.f;
       ok = ok && cudaEventSynchronize(t1) == cudaSuccess && cudaEventElapsedTime(&ms, t0, t1) == cudaSuccess;
-      if (r) total += ms;
+      if (r && ms < fastest) fastest = ms;
     }
     if (!ok) { cudaGetLastError(); continue; }
-    if (log) fprintf(stderr, "[edgerag_b200] linear %d x %d x %d: proposal %d, %.1f us\n", M, N, K,
-                     i, total / 3 * 1000);
-    if (total < best) { best = total; best_i = i; }
+    if (log) fprintf(stderr, "[edgerag_b200] linear %d x %d x %d: proposal %d, %.1f us\n", M, N, K, i, fastest * 1000);
+    if (fastest < best) { best = fastest; best_i = i; }
   }
   cudaEventDestroy(t0);
   cudaEventDestroy(t1);
