@@ -31,7 +31,6 @@ struct Plan {
   cublasLtMatmulHeuristicResult_t candidates[8];
   int n_candidates = 0;
   bool tuned = false;
-  int uses = 0;        // calls outside a stream capture so far
 };
 
 using Key = std::tuple<int, int, int, int, int, int, int, int, size_t>;
@@ -75,13 +74,19 @@ bool tuning_enabled() {
 }
 
 // The library's first choice is not always its fastest algorithm for a shape (the products of a 2,048-token
-// portion: 5 % of the step).  A shape with 1,024 rows or more that keeps coming back is worth a look: on its
-// third use outside a stream capture every proposal runs a few times on the caller's operands (each
-// writes the same product to `out`), every run after a write of more than L2's size so that the weights come
-// from DRAM as they do in a step, timed with events, and the fastest stays.  One choice per shape and
-// process.  Not below 1,024 rows: every odd row count of a serving step (513 to 576 rows) would pay for a
-// trial of its own, and for the 17 to 64 rows of a decode step none of the proposals beat the first.
-constexpr int kTuneFromRows = 1024, kTuneAtUse = 3;
+// portion: 5 % of the step).  A trial of a layer's four shapes costs as much as several steps, so it is for
+// shapes that keep coming back, and the caller knows which those are: it switches trials on (erb_linear_tune)
+// around a run whose shapes it expects to use many times more (the engine: the run before a step's layout is
+// captured into a CUDA graph, which happens when the layout is seen a second time and fixes the algorithms
+// for every replay).  During such a run, outside a stream capture, every proposal for a shape of 1,024 rows
+// or more runs a few times on the caller's operands (each writes the same product to `out`), every run after
+// a write of more than L2's size so that the weights come from DRAM as they do in a step, timed with events;
+// a proposal's fastest of three runs counts, one that is 15 % behind the best so far gets no further runs,
+// and the fastest proposal stays: one choice per shape and process.  Not below 1,024 rows: for the 17 to
+// 64 rows of a decode step none of the proposals beat the first, and when the 513 to 576 rows of serving
+// steps were tried (then with the weights in L2) the choices were slower inside the step.
+constexpr int kTuneFromRows = 1024;
+bool g_tune_now = false;         // set by the caller around a run whose shapes are worth a trial (erb_linear_tune)
 constexpr size_t kFlushBytes = 192u << 20;
 
 int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f32, int accumulate,
@@ -126,7 +131,7 @@ void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void*
   if (p.n_candidates < 2 || M < from_rows || !tuning_enabled()) { p.tuned = true; return; }
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) return;
-  if (++p.uses < kTuneAtUse) return;
+  if (!g_tune_now) return;
   p.tuned = true;
   // In a step the weights of a product come from DRAM (a layer's weights pass through L2 long before
   // the layer runs again), so every timed run starts after a buffer larger than L2 has been written.
@@ -143,7 +148,7 @@ void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void*
     if (c.state != CUBLAS_STATUS_SUCCESS || c.workspaceSize > ws) continue;
     bool ok = true;
     float fastest = 1e30f;
-    for (int r = 0; r < 6 && ok; ++r) {     // one to warm up, five timed: the fastest counts (what disturbs a run only adds)
+    for (int r = 0; r < 4 && ok; ++r) {     // one to warm up, three timed: the fastest counts (what disturbs a run only adds)
       cudaMemsetAsync(flush, r, kFlushBytes, stream);
       cudaEventRecord(t0, stream);
       ok = cublasLtMatmul(g_handle, p.op, &alpha, w, p.a, a, p.b, &beta, out, p.c, out, p.c, &c.algo, workspace, ws,
@@ -152,6 +157,7 @@ void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void*
       float ms = 0.f;
       ok = ok && cudaEventSynchronize(t1) == cudaSuccess && cudaEventElapsedTime(&ms, t0, t1) == cudaSuccess;
       if (r && ms < fastest) fastest = ms;
+      if (r && ms > 1.15f * best) break;    // (no match for the best so far: its other runs are saved)
     }
     if (!ok) { cudaGetLastError(); continue; }
     if (log) fprintf(stderr, "[edgerag_b200] linear %d x %d x %d: proposal %d, %.1f us\n", M, N, K, i, fastest * 1000);
@@ -165,6 +171,13 @@ void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void*
 }
 
 }  // namespace
+
+// Trials of the library's proposals (see tune_plan) on or off for the products that follow.
+ERB_EXPORT int erb_linear_tune(int on) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  g_tune_now = on != 0;
+  return ERB_OK;
+}
 
 // out[M, N] (+)= a[M, K] * w[N, K]^T.  `out_f32` selects a float output in the bfloat16 build;
 // `accumulate` adds to what `out` holds (beta = 1) instead of overwriting it.

@@ -441,8 +441,18 @@ class ModelRunner:
         if len(self._graph_seen) > 8192:
             self._graph_seen.clear()
         self._graph_seen[key] = seen + 1
-        logits = self.model.forward(ctx)
-        if seen >= 1 and len(self._graphs) < self.max_graphs:
+        capture = seen >= 1 and len(self._graphs) < self.max_graphs
+        # The layout has come back and its graph will fix the library's algorithms for every replay: the
+        # run before the capture lets the library's proposals for its large products be timed once.
+        tune = capture and ctx.n_tokens >= kernels.LINEAR_TUNE_FROM_ROWS
+        if tune:
+            kernels.linear_tune(self.dtype, True)
+        try:
+            logits = self.model.forward(ctx)
+        finally:
+            if tune:
+                kernels.linear_tune(self.dtype, False)
+        if capture:
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_counts["own"]
             # No cyclic garbage collection while the stream captures: a collector run could destroy

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "erb_linear_skinny_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "erb_linear_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_linear_tune": [c_int],
     "erb_linear_tc_parts": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_tc_parts_count": [c_int, c_int],
     "erb_residual_add_parts": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
@@ -455,6 +456,18 @@ def linear_rope_store(a: torch.Tensor, weight: torch.Tensor, qkv: torch.Tensor, 
     _call(_fn("gemm", "bfloat16", "erb_linear_skinny_rope"), a.data_ptr(), weight.data_ptr(), qkv.data_ptr(), m, k,
           lda, k, ldo, n_q_heads, n_kv_heads, head_dim, positions.data_ptr(), inv_freq.data_ptr(), slots.data_ptr(),
           k_pages.data_ptr(), v_pages.data_ptr(), page_size, _stream())
+
+
+LINEAR_TUNE_FROM_ROWS = 1024     # rows from which the library's proposals for a shape are timed (as in csrc/gemm.cu)
+
+
+def linear_tune(dtype: torch.dtype, on: bool) -> None:
+    """Switch trials of the library's proposals on or off for the library products (of this element type) that
+    follow: while on, a shape of ``LINEAR_TUNE_FROM_ROWS`` rows or more that has had no trial yet gets one
+    (every proposal timed on the caller's operands with the weights from DRAM; the fastest stays for the
+    process).  A trial costs as much as several steps: it is for a run whose shapes will be used many
+    times more, such as the run before a step's layout is captured into a CUDA graph."""
+    _fn("gemm", _ELEM[dtype], "erb_linear_tune")(int(bool(on)))
 
 
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
