@@ -113,7 +113,7 @@ int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f
   LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws_bytes,
                                                 sizeof(ws_bytes)));
   int found = 0;
-  const int want = (M >= env_int("EDGERAG_B200_TUNE_FROM_ROWS", kTuneFromRows) && tuning_enabled()) ? 8 : 1;   // more than one only where they get timed
+  const int want = (M >= kTuneFromRows && tuning_enabled()) ? 8 : 1;   // more than one only where they get timed
   cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(g_handle, p.op, p.a, p.b, p.c, p.c, pref, want, p.candidates, &found);
   cublasLtMatmulPreferenceDestroy(pref);
   if (st != CUBLAS_STATUS_SUCCESS || found == 0)
@@ -126,9 +126,8 @@ int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f
 }
 
 void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void* out, void* workspace, size_t ws, cudaStream_t stream) {
-  static const int from_rows = env_int("EDGERAG_B200_TUNE_FROM_ROWS", kTuneFromRows);
   static const bool log = env_int("EDGERAG_B200_TUNE_LOG", 0) != 0;
-  if (p.n_candidates < 2 || M < from_rows || !tuning_enabled()) { p.tuned = true; return; }
+  if (p.n_candidates < 2 || M < kTuneFromRows || !tuning_enabled()) { p.tuned = true; return; }
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) return;
   if (!g_tune_now) return;
