@@ -80,6 +80,37 @@ def test_add_rmsnorm(k, dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,rows", [(72, 9), (1001, 5), (2048, 70), (2052, 33), (4096, 130)])
+def test_add_rmsnorm_of_partial_sums(k, dtype, width, rows):
+    """The update given as float32 partial sums [parts, rows, width] (widths for the one-pass, the two-pass and
+    the scalar kernel): the same bits as the norm fed their sum, added in order and rounded to the element
+    type once; rows selected; the plain residual add likewise."""
+    parts = rand((5, rows, width), torch.float32, 31, 0.7)
+    hidden = rand((rows, width), torch.float32, 32, 2.0)
+    weight = rand((width,), torch.float32, 33).add_(1.0)
+    total = parts[0].clone()
+    for s in range(1, 5):
+        total += parts[s]
+    delta = total.to(dtype)
+    want, h_want = torch.empty((rows, width), dtype=dtype, device="cuda"), hidden.clone()
+    k.add_rmsnorm(h_want, weight, want, 2e-5, delta=delta)
+    got, h_got = torch.full((rows, width), float("nan"), dtype=dtype, device="cuda"), hidden.clone()
+    k.add_rmsnorm(h_got, weight, got, 2e-5, delta=parts)
+    assert torch.equal(h_got, h_want) and torch.equal(got, want)
+    picks = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32).cuda()
+    some, h_same = torch.empty((3, width), dtype=dtype, device="cuda"), hidden.clone()
+    k.add_rmsnorm(h_same, weight, some, 2e-5, delta=parts[:, :, :], rows=picks, write_back=False)
+    assert torch.equal(h_same, hidden) and torch.equal(some, want[picks.long()])
+    k.residual_add(h_same, parts, dtype)
+    assert torch.equal(h_same, h_want)
+    # a view of the parts with a stride between them (a scratch buffer made for more rows)
+    roomy = torch.zeros((5, rows + 3, width), dtype=torch.float32, device="cuda")
+    roomy[:, :rows] = parts
+    with pytest.raises(k.KernelError):
+        k.add_rmsnorm(hidden.clone(), weight, got, 2e-5, delta=roomy[:, :rows])       # parts must be contiguous
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("width", [2048, 4096, 2052])
 def test_add_rmsnorm_gives_a_row_the_same_bits_in_any_batch(k, dtype, width):
     """Wide rows are normed by more threads when the batch has few rows and by fewer, busier threads
