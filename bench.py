@@ -172,7 +172,7 @@ def run_ours(args) -> dict:
     engine = Engine.from_config(cfg, weights_seed=0, std=0.02, options=EngineOptions(
         dtype="bfloat16", device="cuda:0", block_size=block, num_blocks=most * pages_per_seq + 8 + 2048 // block,
         max_batch_size=most + 1, chunk_size=2048, max_prefills_per_step=batch, max_step_tokens=2048 * batch + most,
-        max_model_len=context + 8))
+        max_model_len=context + 8, tune_products=True))     # (the prefill step's layout is captured: its products are tuned once)
     runner, cache = engine.runner, engine.cache
     vocab = cfg["vocab_size"]
     gen = torch.Generator().manual_seed(0)
@@ -303,7 +303,8 @@ def run_ours(args) -> dict:
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
             "rope_theta": cfg["rope_theta"], "rms_eps": cfg["rms_norm_eps"], "tied": True, "page_tokens": block,
             "l2": "inputs larger than L2 (weights 3.4 GB + cache), no flush", "points_context": context,
-            "peaks": peak_source, "cuda_graphs": bool(engine.options.cuda_graphs and runner.graphs_enabled),
+            "peaks": peak_source,
+            "cuda_graphs": ("on, tune_products" if engine.options.tune_products else "on") if engine.options.cuda_graphs and runner.graphs_enabled else "off",
         },
         "clocks": clocks.record(), "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill,
         "roofline": roofline, "points": points, "spread": step_spread,

@@ -52,6 +52,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--no-cuda-graphs", action="store_true", help="launch every kernel of every step from the host")
     ap.add_argument("--batch-invariant", action="store_true",
                     help="kernel shapes that do not follow the batch: the same bits for a request whatever shares its step")
+    ap.add_argument("--tune-products", action="store_true",
+                    help="time the library's algorithms for large products once before a step layout is captured (for long runs of equal large steps)")
     ap.add_argument("--prompt-ids", action="append", default=[], metavar="IDS",
                     help="a prompt as token ids, comma or space separated; may be given several times")
     ap.add_argument("--prompt-file", help="a file with one prompt per line (token ids)")
@@ -79,7 +81,8 @@ def main(argv: list[str] | None = None) -> int:
         budget_gib=args.budget_gib or None, kv_fraction=args.kv_fraction, max_batch_size=args.max_batch_size,
         chunk_size=args.chunk_size, max_prefills_per_step=args.max_prefills_per_step,
         max_model_len=args.max_model_len, eos_token_id=args.eos_token_id, seed=args.seed,
-        lookahead=not args.no_lookahead, cuda_graphs=not args.no_cuda_graphs, batch_invariant=args.batch_invariant)
+        lookahead=not args.no_lookahead, cuda_graphs=not args.no_cuda_graphs, batch_invariant=args.batch_invariant,
+        tune_products=args.tune_products)
     t0 = time.perf_counter()
     if args.model is not None:
         engine = Engine.from_pretrained(args.model, options)

@@ -91,6 +91,12 @@ class EngineOptions:
     #: captured steps fill their single-token rows up to the next of a few sizes (1, 2, 4, 8, 16, 24, ...), so
     #: that a change in the number of running requests seldom needs another graph
     pad_decodes: bool = True
+    #: before a step's layout is captured into a CUDA graph, let the library's proposals for its products of
+    #: 1,024 rows or more be timed against each other once (the fastest stays for the process).  A trial
+    #: costs tens of milliseconds (every proposal is a kernel the library has to load): it pays where the same
+    #: large steps run many hundreds of times (prompts served in portions of a fixed size: 5 % of a 2,048-token
+    #: step), and costs where layouts change all the time, so it is off unless asked for
+    tune_products: bool = False
 
 
 @dataclass
@@ -144,7 +150,7 @@ class Engine:
                                  self.device, poison=options.poison_freed_pages)
         self.runner = ModelRunner(model, self.cache, self.pools, max_step_tokens=max_step,
                                   cuda_graphs=options.cuda_graphs, batch_invariant=options.batch_invariant,
-                                  pad_decodes=options.pad_decodes)
+                                  pad_decodes=options.pad_decodes, tune_products=options.tune_products)
         self.scheduler = Scheduler(self.cache, SchedulerConfig(
             max_batch_size=options.max_batch_size, prefill_chunk_size=options.chunk_size,
             max_prefills_per_step=options.max_prefills_per_step, max_step_tokens=max_step,

@@ -154,8 +154,9 @@ class ModelRunner:
 
     def __init__(self, model, cache: CacheManager, pools: DevicePools, max_step_tokens: int,
                  check_status: bool = False, cuda_graphs: bool = False, batch_invariant: bool = False,
-                 pad_decodes: bool = True) -> None:
+                 pad_decodes: bool = True, tune_products: bool = False) -> None:
         self.model = model
+        self.tune_products = bool(tune_products)     # see EngineOptions.tune_products
         self.batch_invariant = bool(batch_invariant)
         #: steps whose tokens are all ids get their single-token sequences (and their wanted rows) filled up
         #: to the next of a few sizes with rows that read one cached key, write nothing and are dropped
@@ -442,9 +443,9 @@ class ModelRunner:
             self._graph_seen.clear()
         self._graph_seen[key] = seen + 1
         capture = seen >= 1 and len(self._graphs) < self.max_graphs
-        # The layout has come back and its graph will fix the library's algorithms for every replay: the
-        # run before the capture lets the library's proposals for its large products be timed once.
-        tune = capture and ctx.n_tokens >= kernels.LINEAR_TUNE_FROM_ROWS
+        # The layout has come back and its graph will fix the library's algorithms for every replay: where
+        # asked for, the run before the capture lets the library's proposals for its large products be timed once.
+        tune = self.tune_products and capture and ctx.n_tokens >= kernels.LINEAR_TUNE_FROM_ROWS
         if tune:
             kernels.linear_tune(self.dtype, True)
         try:

@@ -333,6 +333,11 @@ def linear_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
           int(out.dtype == torch.float32), _stream())
 
 
+#: weights below this size stay with the library at 17 to 64 rows (measured at 64 rows: 960 x 960, 1.8 MB, 4.2 us in
+#: parts against 3.4 us; 960 x 2560, 4.9 MB, 4.3 against 5.9 us; 2048 x 2048, 8.4 MB, 4.5 against 5.8 us)
+PARTS_MIN_WEIGHT_ELEMENTS = 2 << 20
+
+
 def linear_parts_count(a: torch.Tensor, weight: torch.Tensor) -> int:
     """How many partial results ``linear_parts`` leaves for ``a @ weight^T``, or 0 where the product is
     not taken in parts: it is for the bfloat16 rows of a decode step beyond the register kernel's
@@ -344,7 +349,15 @@ def linear_parts_count(a: torch.Tensor, weight: torch.Tensor) -> int:
         return 0
     if not linear_few_rows_supported(a, weight, a.stride(0)) or -(-n // 128) * 2 > _sms(a.device):
         return 0
+    if n * k < PARTS_MIN_WEIGHT_ELEMENTS:
+        return 0
     return _parts_count(n, k)
+
+
+def linear_parts_slices(weight: torch.Tensor) -> int:
+    """The number of slices of k, and so of partial results, that ``linear_parts`` makes for this weight (a
+    function of its shape alone)."""
+    return _parts_count(weight.shape[0], weight.shape[1])
 
 
 @functools.lru_cache(maxsize=256)
@@ -354,14 +367,15 @@ def _parts_count(n: int, k: int) -> int:
 
 def linear_parts(a: torch.Tensor, weight: torch.Tensor, parts: torch.Tensor) -> None:
     """``parts[s] = a[:, slice s of k] @ weight[:, slice s of k]^T`` in float32 for the
-    ``linear_parts_count`` slices of k; their sum in order is the product (``add_rmsnorm`` and
-    ``residual_add`` take them as they are)."""
+    ``linear_parts_slices`` slices of k; their sum in order is the product (``add_rmsnorm`` and
+    ``residual_add`` take them as they are).  Up to ``TC_MAX_ROWS`` bfloat16 rows, n a multiple of 4."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
     _need(parts, "parts", torch.float32)
     m, k = a.shape
     n = weight.shape[0]
-    if weight.shape[1] != k or a.stride(1) != 1 or tuple(parts.shape) != (linear_parts_count(a, weight), m, n):
-        raise KernelError("linear_parts: shapes disagree or the product is not taken in parts")
+    if (weight.shape[1] != k or a.stride(1) != 1 or m > TC_MAX_ROWS or n % 4 or not linear_few_rows_supported(a, weight, a.stride(0))
+            or tuple(parts.shape) != (linear_parts_slices(weight), m, n)):
+        raise KernelError("linear_parts: shapes disagree or the operands are not supported")
     _call(_fn_tc("erb_linear_tc_parts"), a.data_ptr(), weight.data_ptr(), parts.data_ptr(), m, n, k, a.stride(0), k, n,
           _stream())
 

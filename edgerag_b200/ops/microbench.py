@@ -159,9 +159,7 @@ def linear(a) -> dict:
     x = torch.randn((a.m, a.k), device="cuda").to(dtype)
     out = torch.empty((a.m, a.n), device="cuda", dtype=torch.float32 if a.out32 else dtype)
     out_glu = torch.empty((a.m, a.n // 2), device="cuda", dtype=dtype) if a.glu else None
-    n_parts = kernels.linear_parts_count(x, ws[0]) if a.parts else 0
-    if a.parts and not n_parts:
-        raise SystemExit("this product is not taken in parts (17 to 64 bfloat16 rows, a weight of few rows)")
+    n_parts = kernels.linear_parts_slices(ws[0]) if a.parts else 0
     parts = torch.empty((n_parts, a.m, a.n), device="cuda", dtype=torch.float32) if n_parts else None
     state = {"i": 0}
 

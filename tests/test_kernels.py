@@ -132,7 +132,9 @@ def test_product_in_parts_and_the_norm_that_adds_them(k):
     of rows, and the residual add + norm that takes the parts against the same norm fed their sum."""
     for m, n, kk in ((17, 2048, 2048), (64, 2048, 8192), (40, 960, 2560), (33, 204, 1032), (64, 576, 1536), (24, 100, 136)):
         a, w = rand((m, kk), torch.bfloat16, 180 + m, 0.5), rand((n, kk), torch.bfloat16, 181 + m, 0.5)
-        count = k.linear_parts_count(a, w)
+        count = k.linear_parts_slices(w)
+        # the dispatcher takes a product in parts from 17 rows on, and only against weights large enough to pay
+        assert k.linear_parts_count(a, w) == (count if n * kk >= k.PARTS_MIN_WEIGHT_ELEMENTS else 0)
         assert count >= 1 and k.linear_parts_count(a[:16], w) == 0
         parts = torch.full((count, m, n), float("nan"), dtype=torch.float32, device="cuda")
         k.linear_parts(a, w, parts)

@@ -97,14 +97,13 @@ def test_cuttings_at_real_layer_sizes(which, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("which,dtype", [("2b", "bfloat16"), ("500m", "bfloat16"), ("256m", "float32")])
-def test_cuttings_replayed_from_cuda_graphs(which, dtype, tmp_path, monkeypatch):
+def test_cuttings_replayed_from_cuda_graphs(which, dtype, tmp_path):
     """The same cuttings three times over in one process with CUDA graphs on, as serving runs: a layout is
     captured the second time it is seen and replayed from then on, so the third pass (and the decode
     steps of every pass) come out of graphs.  Same bands against the plain model; and a replayed step
-    gives the bits of the step that was launched kernel by kernel.  (The two runs are two processes: the
-    library's algorithm for a product is each process's own choice among the library's proposals, by
-    timing them, unless EDGERAG_B200_NO_TUNE is set; it is set here, so that both take the first proposal.)"""
-    monkeypatch.setenv("EDGERAG_B200_NO_TUNE", "1")
+    gives the bits of the step that was launched kernel by kernel.  (The two runs are two processes; both take
+    the library's first proposal for every product, the engine's default: with ``tune_products`` each process
+    would keep its own choice among the proposals, by timing them.)"""
     import re
     import shutil
 
