@@ -87,6 +87,7 @@ bool tuning_enabled() {
 // steps were tried (then with the weights in L2) the choices were slower inside the step.
 constexpr int kTuneFromRows = 1024;
 bool g_tune_now = false;         // set by the caller around a run whose shapes are worth a trial (erb_linear_tune)
+int g_trials = 0;                // trials run so far in this process
 constexpr size_t kFlushBytes = 192u << 20;
 
 int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f32, int accumulate,
@@ -126,12 +127,13 @@ int make_plan(Plan& p, int M, int N, int K, int lda, int ldw, int ldo, int out_f
 }
 
 void tune_plan(Plan& p, int M, int N, int K, const void* a, const void* w, void* out, void* workspace, size_t ws, cudaStream_t stream) {
-  static const bool log = env_int("EDGERAG_B200_TUNE_LOG", 0) != 0;
   if (p.n_candidates < 2 || M < kTuneFromRows || !tuning_enabled()) { p.tuned = true; return; }
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) return;
   if (!g_tune_now) return;
   p.tuned = true;
+  ++g_trials;
+  const bool log = env_int("EDGERAG_B200_TUNE_LOG", 0) != 0;
   // In a step the weights of a product come from DRAM (a layer's weights pass through L2 long before
   // the layer runs again), so every timed run starts after a buffer larger than L2 has been written.
   void* flush = nullptr;
@@ -176,6 +178,12 @@ ERB_EXPORT int erb_linear_tune(int on) {
   std::lock_guard<std::mutex> lock(g_mutex);
   g_tune_now = on != 0;
   return ERB_OK;
+}
+
+// How many shapes have had a trial in this process.
+ERB_EXPORT int erb_linear_trials() {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  return g_trials;
 }
 
 // out[M, N] (+)= a[M, K] * w[N, K]^T.  `out_f32` selects a float output in the bfloat16 build;

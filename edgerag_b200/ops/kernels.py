@@ -41,6 +41,7 @@ _SIGNATURES = {
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "erb_linear_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_tune": [c_int],
+    "erb_linear_trials": [],
     "erb_linear_tc_parts": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_tc_parts_count": [c_int, c_int],
     "erb_residual_add_parts": [c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p],
@@ -482,6 +483,11 @@ def linear_tune(dtype: torch.dtype, on: bool) -> None:
     process).  A trial costs as much as several steps: it is for a run whose shapes will be used many
     times more, such as the run before a step's layout is captured into a CUDA graph."""
     _fn("gemm", _ELEM[dtype], "erb_linear_tune")(int(bool(on)))
+
+
+def linear_trials(dtype: torch.dtype) -> int:
+    """How many product shapes (of this element type) have had a trial in this process."""
+    return int(_fn("gemm", _ELEM[dtype], "erb_linear_trials")())
 
 
 def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
