@@ -379,3 +379,109 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
                 diff = (out - want[k]).abs()
                 # a token whose two best router logits lie close may go to another expert in bfloat16: judge the rest
                 assert float(diff.mean()) <= 0.01 * scale and float((diff.max(dim=1).values <= 0.03 * scale).float().mean()) >= 0.8
+
+
+def test_toy_feed_forward_that_hands_over_partial_sums(tmp_path):
+    """A feed-forward defined here whose last product leaves float32 partial sums over slices of k
+    (``kernels.linear_parts``) instead of finished rows: the norm that follows (the next layer's, or the final
+    one) adds them, so nothing outside the part changes.  Stepped in portions of 1 to 40 rows beside another
+    request, in bfloat16 (partial sums) and in float32 (finished rows), against a whole-sequence computation."""
+    from edgerag_b200 import Engine
+    from edgerag_b200.config import register_architecture
+    from edgerag_b200.config.registry import architecture_of
+    from edgerag_b200.engine.step import StepEntry
+    from edgerag_b200.models.decoder import DecoderModel
+    from edgerag_b200.ops import kernels
+    from edgerag_b200.parts.base import FeedForward, LayerCall, LayerSpec, ModelPlan, PartSpec, WeightSpec, register_part
+    from edgerag_b200.weights.loader import write_model_folder
+    import helpers
+    import plain_llama as plain
+
+    h, nq, nkv, d, inter, vocab, layers, theta = 48, 3, 1, 16, 200, 91, 2, 500.0
+    handed_over = []
+
+    @register_part("ffn", "toy_parts")
+    class ToyPartsFeedForward(FeedForward):
+        """y = down(relu(up(x))); up to 64 bfloat16 rows the down product is handed over as partial sums."""
+
+        def __init__(self, hidden, intermediate, dtype, device):
+            self.hidden, self.intermediate, self.dtype, self.device = hidden, intermediate, dtype, device
+
+        def weight_specs(self):
+            return [WeightSpec("up.weight", (self.intermediate, self.hidden)), WeightSpec("down.weight", (self.hidden, self.intermediate))]
+
+        def load_weights(self, tensors):
+            self.up = tensors["up.weight"].to(device=self.device, dtype=self.dtype).contiguous()
+            self.down = tensors["down.weight"].to(device=self.device, dtype=self.dtype).contiguous()
+
+        def forward(self, x, ctx):
+            n = x.shape[0]
+            mid = torch.empty((n, self.intermediate), dtype=self.dtype, device=x.device)
+            kernels.linear(x, self.up, mid)
+            mid = torch.relu(mid)
+            if self.dtype == torch.bfloat16 and n <= kernels.TC_MAX_ROWS:
+                parts = torch.empty((kernels.linear_parts_slices(self.down), n, self.hidden), dtype=torch.float32, device=x.device)
+                kernels.linear_parts(mid, self.down, parts)
+                handed_over.append(parts.shape[0])
+                return parts
+            y = torch.empty((n, self.hidden), dtype=self.dtype, device=x.device)
+            kernels.linear(mid, self.down, y)
+            return y
+
+    def make_plan(raw):
+        norm = lambda p: PartSpec("rmsnorm", {"size": h, "eps": 1e-5}, p)   # noqa: E731
+        rope = PartSpec("rope_halves", {"head_dim": d, "theta": theta})
+        specs = []
+        for i in range(layers):
+            mixer = PartSpec("attention", {"hidden": h, "n_q_heads": nq, "n_kv_heads": nkv, "head_dim": d, "position": rope}, "self_attn.")
+            ffn = PartSpec("toy_parts", {"hidden": h, "intermediate": inter}, "ff.")
+            specs.append(LayerSpec(f"layers.{i}.", PartSpec("prenorm"), norm("ln1."), mixer, norm("ln2."), ffn))
+        return ModelPlan(h, vocab, PartSpec("table", {"vocab": vocab, "hidden": h}, "embed_tokens."), specs,
+                         [LayerCall(i, i) for i in range(layers)], norm("norm."),
+                         PartSpec("linear", {"vocab": vocab, "hidden": h, "tied_to": None}, "lm_head."))
+
+    register_architecture("ToyPartsForCausalLM", lambda raw, where: raw, make_plan)
+    raw = {"architectures": ["ToyPartsForCausalLM"]}
+    specs = DecoderModel(architecture_of(raw).make_plan(raw), torch.float32, torch.device("cpu")).weight_specs()
+    folder = write_model_folder(tmp_path / "parts", raw, specs, seed=13, std=0.2, norm_jitter=0.1, dtype=torch.float32)
+    w = plain.read_weights(folder)
+    cfg = {"n_q": nq, "n_kv": nkv, "head_dim": d, "theta": theta}
+
+    def whole(seq):
+        x = w["model.embed_tokens.weight"][torch.tensor(seq)]
+        pos = torch.arange(len(seq))
+        for i in range(layers):
+            p = f"model.layers.{i}."
+            a = p + "self_attn."
+            x = x + plain.attention(plain.rms_norm(x, w[p + "ln1.weight"], 1e-5), pos, w[a + "q_proj.weight"], w[a + "k_proj.weight"],
+                                    w[a + "v_proj.weight"], w[a + "o_proj.weight"], cfg)
+            y = plain.rms_norm(x, w[p + "ln2.weight"], 1e-5)
+            x = x + torch.relu(y @ w[p + "ff.up.weight"].T) @ w[p + "ff.down.weight"].T
+        return plain.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["lm_head.weight"].T
+
+    seqs = {"x": torch.randint(0, vocab, (70,), generator=torch.Generator().manual_seed(3)).tolist(),
+            "y": torch.randint(0, vocab, (31,), generator=torch.Generator().manual_seed(4)).tolist()}
+    want = {k: whole(v) for k, v in seqs.items()}
+    plan = [{"x": 9}, {"x": 2, "y": 17}, {"x": 1, "y": 1}, {"y": 13}, {"x": 40}, {"x": 18}]
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine.from_pretrained(folder, dtype=dtype, block_size=4, num_blocks=60, max_batch_size=3)
+        runner = engine.runner
+        runner.admit("x"), runner.admit("y")
+        got, fed = {"x": [], "y": []}, {"x": 0, "y": 0}
+        for step in plan:
+            entries = [StepEntry(k, tokens=seqs[k][fed[k]: fed[k] + n], want=list(range(n))) for k, n in step.items()]
+            logits = runner.step(entries).cpu()
+            row = 0
+            for k, n in step.items():
+                got[k].append(logits[row: row + n].clone())
+                row += n
+                fed[k] += n
+        for k in seqs:
+            out = torch.cat(got[k])
+            if dtype == "float32":
+                torch.testing.assert_close(out, want[k], atol=2e-4, rtol=2e-4)
+            else:
+                scale = float(want[k].abs().max())
+                diff = (out - want[k]).abs()
+                assert float(diff.max()) <= helpers.BF16_FRACTION * scale and float(diff.mean()) <= helpers.BF16_MEAN_FRACTION * scale
+    assert handed_over and min(handed_over) >= 2       # k = 200 is cut into more than one slice
